@@ -358,8 +358,18 @@ extern "C" int32_t cfb200_gemm_bf16_nt(const void* A, const void* B, size_t M, s
 // H (K x K f32) = X^T X / T for X [T, K] bf16.  xt_workspace: T*K bf16 (the transposed copy).
 extern "C" size_t cfb200_gptq_hessian_workspace_bytes(size_t T, size_t K) { return T * K * 2; }
 
+extern "C" int32_t cfb200_gptq_hessian_scaled(const void* X, size_t T, size_t K, float alpha, float* H, void* xt_workspace,
+                                              size_t workspace_bytes, int32_t* error_flag, void* stream);
+
 extern "C" int32_t cfb200_gptq_hessian(const void* X, size_t T, size_t K, float* H, void* xt_workspace, size_t workspace_bytes,
                                        int32_t* error_flag, void* stream) {
+  CFB_CHECK_ARG(T > 0, "bad argument");
+  return cfb200_gptq_hessian_scaled(X, T, K, 1.0f / (float)T, H, xt_workspace, workspace_bytes, error_flag, stream);
+}
+
+// H = alpha * X^T X: the building block of a Hessian accumulated over several token shards (alpha = 1 / total tokens).
+extern "C" int32_t cfb200_gptq_hessian_scaled(const void* X, size_t T, size_t K, float alpha, float* H, void* xt_workspace,
+                                              size_t workspace_bytes, int32_t* error_flag, void* stream) {
   CFB_CHECK_ARG(X && H && T > 0 && K > 0, "bad argument");
   CFB_CHECK_ARG(T % 8 == 0, "the token count must be a multiple of 8 (got %zu)", T);
   if (!xt_workspace || workspace_bytes < T * K * 2) return set_error(CFB200_ERR_WORKSPACE, "gptq_hessian needs %zu bytes of workspace", T * K * 2);
@@ -368,7 +378,7 @@ extern "C" int32_t cfb200_gptq_hessian(const void* X, size_t T, size_t K, float*
   transpose_bf16_kernel<<<tg, tb, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(X), T, K, reinterpret_cast<__nv_bfloat16*>(xt_workspace));
   CFB_LAUNCH_CHECK();
   CFB_CUDA(cudaMemsetAsync(H, 0, K * K * sizeof(float), st));
-  int32_t rc = cfb200_gemm_bf16_nt(xt_workspace, xt_workspace, K, K, T, 1.0f / (float)T, H, 1, 1, error_flag, stream);
+  int32_t rc = cfb200_gemm_bf16_nt(xt_workspace, xt_workspace, K, K, T, alpha, H, 1, 1, error_flag, stream);
   if (rc) return rc;
   dim3 mg((unsigned)((K + 15) / 16), (unsigned)((K + 15) / 16)), mb(16, 16);
   mirror_upper_kernel<<<mg, mb, 0, st>>>(H, (int)K);

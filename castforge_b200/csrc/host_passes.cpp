@@ -9,6 +9,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <mutex>
 #include <set>
 
 #include "../../include/cfb200.h"
@@ -233,6 +234,7 @@ struct Plan {
 
 struct Slot { void *in = nullptr, *out = nullptr, *scratch = nullptr; size_t in_cap = 0, out_cap = 0, scratch_cap = 0; cudaEvent_t free_ev = nullptr; bool used = false; };
 struct Engine {
+  std::mutex busy;  // one pipeline at a time per device: the slots and streams below are shared by every caller
   int dev = -1;
   cudaStream_t s_h2d = nullptr, s_cmp = nullptr, s_d2h = nullptr;
   Slot slots[3];
@@ -257,6 +259,8 @@ bool grow(void** p, size_t* cap, size_t need, std::string* err) {
   return true;
 }
 Engine* engine(std::string* err) {
+  static std::mutex init_mutex;
+  std::lock_guard<std::mutex> lock(init_mutex);
   int dev = 0;
   if (!ck(cudaGetDevice(&dev), err, "cudaGetDevice")) return nullptr;
   if (dev < 0 || dev >= 16) { *err = "device ordinal out of range"; return nullptr; }
@@ -330,6 +334,8 @@ bool run_quantize_on_store(TensorStore& store, const QuantizeConfig& cfg, PassRe
 
   Engine* eng = engine(err);
   if (!eng) return false;
+  // Calls from several host threads are allowed (the reference's C ABI is re-entrant); on one device they take turns.
+  std::lock_guard<std::mutex> engine_lock(eng->busy);
   const int bits = cfg.bits;
   const bool awq = cfg.awq_salient || s == "awq";
 
@@ -530,6 +536,11 @@ bool run_quantize_on_store(TensorStore& store, const QuantizeConfig& cfg, PassRe
   for (cudaEvent_t ev : evs) cudaEventDestroy(ev);
   if (!ok_all) return false;
   if (!ck(fin, err, "device pipeline")) return false;
+  if (kind == kWeight) {  // the cooperative A1 launch reports an expired wait through a device flag, not a return code
+    int32_t flag = 0;
+    if (cfb200_quant_sym_status(&flag) != 0) { *err = std::string("device status: ") + cfb200_last_error(); return false; }
+    if (flag != 0) { *err = "the quantize kernel gave up a bounded wait on this device: results are incomplete"; return false; }
+  }
 
   // ---- publish results into the store ----
   for (size_t t = 0; t < todo.size(); ++t) {

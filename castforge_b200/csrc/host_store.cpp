@@ -396,6 +396,12 @@ static bool walk_safetensors_header(const char* hdr, size_t hl, uint64_t body_le
     const JVal *jd = h.find("dtype"), *js = h.find("shape"), *jo = h.find("data_offsets");
     if (h.kind != JVal::Obj || !jd || jd->kind != JVal::Str || !js || js->kind != JVal::Arr || !jo || jo->kind != JVal::Arr || jo->arr.size() != 2)
       return bad("Malformed header entry for tensor `" + kv.first + "`");
+    // data_offsets are `usize` in the reference's header struct: anything but a non-negative integer is a parse error there
+    for (int k = 0; k < 2; ++k) {
+      const JVal& o = jo->arr[k];
+      if (o.kind != JVal::Num || !(o.num >= 0.0) || o.num > 9007199254740992.0 || o.num != (double)(uint64_t)o.num)
+        return bad("Invalid data_offsets entry for tensor `" + kv.first + "`: expected a non-negative integer");
+    }
     const size_t start = (size_t)jo->arr[0].num, stop = (size_t)jo->arr[1].num;
     if (stop > body_len || start > stop) return bad("Invalid data_offsets [" + std::to_string(start) + ", " + std::to_string(stop) + "] for tensor `" + kv.first + "`");
     if (start < stop)
@@ -418,10 +424,11 @@ static bool walk_safetensors_header(const char* hdr, size_t hl, uint64_t body_le
     else if (dt == "F16") e.dtype = DType::F16;
     else if (dt == "BF16") e.dtype = DType::BF16;
     else if (dt == "I8") e.dtype = DType::I8;
-    else if (dt == "U8") e.dtype = DType::U8;
-    else return bad("Unsupported safetensors dtype `" + dt + "` for tensor `" + kv.first + "`");
+    else e.dtype = DType::U8;  // I64, I32, F64, BOOL, ...: kept as the raw bytes of the slice (tensor_store.rs:742-750)
     const size_t nbytes = stop - start;
-    if (nbytes != elems * dtype_bytes(e.dtype) && !(e.dtype == DType::U8))
+    // Stricter than the reference on purpose: it only asks for a multiple of the element size, but the passes here
+    // copy num_elements() * size bytes of a float / I8 entry to the device, so the two must agree.
+    if (e.dtype != DType::U8 && nbytes != elems * dtype_bytes(e.dtype))
       return bad("Byte length " + std::to_string(nbytes) + " does not match shape of tensor `" + kv.first + "`");
     if (const JVal* sc = h.find("scale")) {
       if (sc->kind == JVal::Num) { e.quantized = true; e.scale = (float)sc->num; }

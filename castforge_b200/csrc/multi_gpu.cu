@@ -1,0 +1,356 @@
+// Multi-GPU side of the quantize-and-execute path: one communicator per GPU (one process per GPU, or one host thread
+// per GPU inside one process), NCCL for the three exchanges the path has.
+//
+//   whole-model quantization   tensors go to ranks whole (largest first); a tensor larger than the split threshold is cut
+//                              into row blocks, and for a per-tensor scale the ranks combine their partial absmax with a
+//                              MAX all-reduce of ONE float per split tensor.  Codes never leave their GPU.
+//   W4A16 / FP8 GEMM           column-parallel: every rank owns N/world output columns of W with their scales / zero
+//                              points, runs the tensor-core kernel on its own memory, then ncclAllGather brings the
+//                              M x N/world bf16 blocks together in every rank's own memory.
+//   GPTQ                       output rows are sharded, U is replicated; the Hessian may be accumulated token-parallel
+//                              and summed with one all-reduce of K x K floats.
+//
+// The reference only stamps `castforge.all_gather` / `castforge.all_reduce` attributes on its graph
+// (src/passes/distributed/spmd.rs:416-478) and evaluates them as the identity (src/codegen/eval.rs:1449-1455); there is
+// no communication code to follow.  NCCL is opened at run time (dlopen of libnccl.so.2), so the library loads and every
+// single-GPU entry point works on a machine without NCCL; only the calls below need it.  No kernel here is handed a
+// pointer into another GPU's memory.
+#include <dlfcn.h>
+#include <nccl.h>
+#include <string.h>
+
+#include <algorithm>
+#include <mutex>
+#include <vector>
+
+#include "common.cuh"
+
+struct cfb200_comm {
+  ncclComm_t nccl = nullptr;
+  int world = 1, rank = 0, device = 0;
+};
+
+namespace cfb {
+namespace {
+
+struct NcclApi {
+  void* handle = nullptr;
+  decltype(&ncclGetUniqueId) GetUniqueId = nullptr;
+  decltype(&ncclCommInitRank) CommInitRank = nullptr;
+  decltype(&ncclCommInitAll) CommInitAll = nullptr;
+  decltype(&ncclCommDestroy) CommDestroy = nullptr;
+  decltype(&ncclAllGather) AllGather = nullptr;
+  decltype(&ncclAllReduce) AllReduce = nullptr;
+  decltype(&ncclGroupStart) GroupStart = nullptr;
+  decltype(&ncclGroupEnd) GroupEnd = nullptr;
+  decltype(&ncclGetErrorString) GetErrorString = nullptr;
+  decltype(&ncclGetVersion) GetVersion = nullptr;
+};
+
+NcclApi g_nccl;
+std::mutex g_nccl_mutex;
+
+// Opens NCCL once.  A process that already carries libnccl.so.2 (PyTorch loads its own copy) gets that copy back.
+int32_t nccl_api(const NcclApi** out) {
+  std::lock_guard<std::mutex> lock(g_nccl_mutex);
+  if (!g_nccl.handle) {
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return set_error(CFB200_ERR_UNSUPPORTED, "NCCL is not available: %s", dlerror());
+    NcclApi a;
+    a.handle = h;
+#define CFB_SYM(field, name)                                                                         \
+  a.field = reinterpret_cast<decltype(a.field)>(dlsym(h, name));                                     \
+  if (!a.field) return set_error(CFB200_ERR_UNSUPPORTED, "NCCL symbol %s is missing", name)
+    CFB_SYM(GetUniqueId, "ncclGetUniqueId");
+    CFB_SYM(CommInitRank, "ncclCommInitRank");
+    CFB_SYM(CommInitAll, "ncclCommInitAll");
+    CFB_SYM(CommDestroy, "ncclCommDestroy");
+    CFB_SYM(AllGather, "ncclAllGather");
+    CFB_SYM(AllReduce, "ncclAllReduce");
+    CFB_SYM(GroupStart, "ncclGroupStart");
+    CFB_SYM(GroupEnd, "ncclGroupEnd");
+    CFB_SYM(GetErrorString, "ncclGetErrorString");
+    CFB_SYM(GetVersion, "ncclGetVersion");
+#undef CFB_SYM
+    g_nccl = a;
+  }
+  *out = &g_nccl;
+  return CFB200_OK;
+}
+
+#define CFB_NCCL(api, call)                                                                            \
+  do {                                                                                                 \
+    ncclResult_t r__ = (call);                                                                         \
+    if (r__ != ncclSuccess) return set_error(CFB200_ERR_CUDA, "%s failed: %s", #call, (api)->GetErrorString(r__)); \
+  } while (0)
+
+// gathered [world][M][Nl] (what ncclAllGather leaves) -> row-major [M][world * Nl], 16 bytes per thread
+__global__ void interleave_blocks_kernel(const uint4* __restrict__ gathered, uint4* __restrict__ out, size_t M, size_t vec_per_row_local,
+                                         int world) {
+  const size_t total = (size_t)world * M * vec_per_row_local;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t v = i % vec_per_row_local, rm = i / vec_per_row_local;
+    const size_t m = rm % M, r = rm / M;
+    out[(m * world + r) * vec_per_row_local + v] = gathered[i];
+  }
+}
+
+inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// local [M, Nl] block (elem_bytes per element) -> every rank's C [M, world * Nl] (layout 0) or [world][M][Nl] (layout 1)
+int32_t gather_columns(cfb200_comm* comm, const void* part, size_t M, size_t Nl, size_t elem_bytes, void* C, int32_t layout,
+                       void* gather_ws, cudaStream_t st) {
+  const NcclApi* api;
+  int32_t rc = nccl_api(&api);
+  if (rc) return rc;
+  const size_t block_bytes = M * Nl * elem_bytes;
+  const bool direct = layout == 1 || M == 1 || comm->world == 1;  // the gathered order already is the wanted order
+  void* dst = direct ? C : gather_ws;
+  CFB_NCCL(api, api->AllGather(part, dst, block_bytes, ncclInt8, comm->nccl, st));
+  if (!direct) {
+    const size_t vpr = Nl * elem_bytes / 16;
+    const size_t total = (size_t)comm->world * M * vpr;
+    size_t blocks = (total + 255) / 256, cap = (size_t)sm_count() * 8;
+    interleave_blocks_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(reinterpret_cast<const uint4*>(gather_ws),
+                                                                                    reinterpret_cast<uint4*>(C), M, vpr, comm->world);
+    CFB_LAUNCH_CHECK();
+  }
+  return CFB200_OK;
+}
+
+}  // namespace
+}  // namespace cfb
+
+using namespace cfb;
+
+// ---- communicators --------------------------------------------------------------------------------------------------
+extern "C" int32_t cfb200_comm_unique_id(void* id_out_128_host) {
+  CFB_CHECK_ARG(id_out_128_host != nullptr, "NULL argument");
+  static_assert(sizeof(ncclUniqueId) == 128, "the id travels as 128 opaque bytes");
+  const NcclApi* api;
+  int32_t rc = nccl_api(&api);
+  if (rc) return rc;
+  ncclUniqueId id;
+  CFB_NCCL(api, api->GetUniqueId(&id));
+  memcpy(id_out_128_host, &id, sizeof id);
+  return CFB200_OK;
+}
+
+extern "C" int32_t cfb200_comm_init(const void* id_128_host, int32_t world, int32_t rank, cfb200_comm** comm_out) {
+  CFB_CHECK_ARG(id_128_host && comm_out, "NULL argument");
+  CFB_CHECK_ARG(world >= 1 && rank >= 0 && rank < world, "bad world / rank (%d, %d)", world, rank);
+  *comm_out = nullptr;
+  const NcclApi* api;
+  int32_t rc = nccl_api(&api);
+  if (rc) return rc;
+  ncclUniqueId id;
+  memcpy(&id, id_128_host, sizeof id);
+  cfb200_comm* c = new cfb200_comm;
+  c->world = world;
+  c->rank = rank;
+  if (cudaGetDevice(&c->device) != cudaSuccess) { delete c; return set_error(CFB200_ERR_CUDA, "cudaGetDevice failed"); }
+  ncclResult_t r = api->CommInitRank(&c->nccl, world, id, rank);
+  if (r != ncclSuccess) { delete c; return set_error(CFB200_ERR_CUDA, "ncclCommInitRank failed: %s", api->GetErrorString(r)); }
+  *comm_out = c;
+  return CFB200_OK;
+}
+
+extern "C" int32_t cfb200_comm_init_local(int32_t ndev, const int32_t* devices, cfb200_comm** comms_out) {
+  CFB_CHECK_ARG(ndev >= 1 && ndev <= 64 && comms_out, "bad arguments");
+  const NcclApi* api;
+  int32_t rc = nccl_api(&api);
+  if (rc) return rc;
+  std::vector<int> devs(ndev);
+  for (int i = 0; i < ndev; ++i) devs[i] = devices ? devices[i] : i;
+  std::vector<ncclComm_t> raw(ndev, nullptr);
+  CFB_NCCL(api, api->CommInitAll(raw.data(), ndev, devs.data()));
+  for (int i = 0; i < ndev; ++i) {
+    cfb200_comm* c = new cfb200_comm;
+    c->nccl = raw[i];
+    c->world = ndev;
+    c->rank = i;
+    c->device = devs[i];
+    comms_out[i] = c;
+  }
+  return CFB200_OK;
+}
+
+extern "C" int32_t cfb200_comm_world(const cfb200_comm* comm) { return comm ? comm->world : 0; }
+extern "C" int32_t cfb200_comm_rank(const cfb200_comm* comm) { return comm ? comm->rank : -1; }
+
+extern "C" void cfb200_comm_free(cfb200_comm* comm) {
+  if (!comm) return;
+  const NcclApi* api;
+  if (comm->nccl && nccl_api(&api) == CFB200_OK) api->CommDestroy(comm->nccl);
+  delete comm;
+}
+
+extern "C" int32_t cfb200_nccl_version(int32_t* version_out) {
+  CFB_CHECK_ARG(version_out != nullptr, "NULL argument");
+  const NcclApi* api;
+  int32_t rc = nccl_api(&api);
+  if (rc) return rc;
+  int v = 0;
+  CFB_NCCL(api, api->GetVersion(&v));
+  *version_out = v;
+  return CFB200_OK;
+}
+
+// ---- placement (pure host arithmetic, identical on every rank: nothing is exchanged) -------------------------------------
+extern "C" int32_t cfb200_shard_assign(int32_t count, const size_t* nbytes, int32_t world, size_t split_min_bytes, int32_t* owner) {
+  CFB_CHECK_ARG(count >= 0 && world >= 1 && (count == 0 || (nbytes && owner)), "bad arguments");
+  std::vector<int> order;
+  std::vector<unsigned long long> load(world, 0);
+  for (int i = 0; i < count; ++i) {
+    if (world > 1 && split_min_bytes > 0 && nbytes[i] >= split_min_bytes) {
+      owner[i] = -1;  // cut into row blocks: every rank gets 1/world of it
+      for (int r = 0; r < world; ++r) load[r] += nbytes[i] / world;
+    } else order.push_back(i);
+  }
+  // largest first onto the least-loaded rank; equal sizes keep store order, ties go to the lowest rank
+  std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return nbytes[a] > nbytes[b]; });
+  for (int i : order) {
+    int best = 0;
+    for (int r = 1; r < world; ++r)
+      if (load[r] < load[best]) best = r;
+    owner[i] = best;
+    load[best] += nbytes[i];
+  }
+  return CFB200_OK;
+}
+
+extern "C" int32_t cfb200_shard_row_range(size_t rows, int32_t world, int32_t rank, size_t align, size_t* row_begin, size_t* row_end) {
+  CFB_CHECK_ARG(world >= 1 && rank >= 0 && rank < world && align >= 1 && row_begin && row_end, "bad arguments");
+  const size_t units = (rows + align - 1) / align, base = units / world, extra = units % world;
+  const size_t lo = (size_t)rank * base + ((size_t)rank < extra ? (size_t)rank : extra);
+  const size_t hi = lo + base + ((size_t)rank < extra ? 1 : 0);
+  *row_begin = lo * align < rows ? lo * align : rows;
+  *row_end = hi * align < rows ? hi * align : rows;
+  return CFB200_OK;
+}
+
+// ---- A1 over a sharded store --------------------------------------------------------------------------------------------
+extern "C" int32_t cfb200_quant_sym_tensors_sharded(cfb200_comm* comm, int32_t count, const void* const* srcs, int32_t src_dtype,
+                                                    const size_t* ns, const int32_t* is_row_block, int32_t bits,
+                                                    int8_t* const* codes, float* scale_absmax, void* stream) {
+  CFB_CHECK_ARG(comm != nullptr, "NULL communicator");
+  CFB_CHECK_ARG(count >= 0, "negative count");
+  if (count == 0) return CFB200_OK;
+  CFB_CHECK_ARG(srcs && ns && codes && scale_absmax, "NULL argument");
+  cudaStream_t st = (cudaStream_t)stream;
+  std::vector<int> w_idx, blocks;
+  for (int i = 0; i < count; ++i) {
+    if (is_row_block && is_row_block[i]) blocks.push_back(i);
+    else w_idx.push_back(i);
+  }
+  int32_t rc = CFB200_OK;
+  // 1. row blocks: partial absmax on this rank, then one MAX all-reduce of one float per split tensor.  Every rank
+  //    passes the split tensors in the same order (an empty block takes part with absmax 0).
+  for (int i : blocks) {
+    if (ns[i]) rc = cfb200_absmax(srcs[i], src_dtype, ns[i], scale_absmax + 2 * i + 1, st);
+    else rc = cudaMemsetAsync(scale_absmax + 2 * i, 0, 2 * sizeof(float), st) == cudaSuccess ? CFB200_OK : set_error(CFB200_ERR_CUDA, "cudaMemsetAsync failed");
+    if (rc) return rc;
+  }
+  if (!blocks.empty() && comm->world > 1) {
+    const NcclApi* api;
+    rc = nccl_api(&api);
+    if (rc) return rc;
+    CFB_NCCL(api, api->GroupStart());
+    for (int i : blocks) {
+      ncclResult_t r = api->AllReduce(scale_absmax + 2 * i + 1, scale_absmax + 2 * i + 1, 1, ncclFloat32, ncclMax, comm->nccl, st);
+      if (r != ncclSuccess) { api->GroupEnd(); return set_error(CFB200_ERR_CUDA, "ncclAllReduce failed: %s", api->GetErrorString(r)); }
+    }
+    CFB_NCCL(api, api->GroupEnd());
+  }
+  // 2. whole tensors: the list kernel on every maximal run of consecutive whole tensors (results land in place);
+  //    it runs while the all-reduce above is still in flight on the same stream order
+  for (size_t k = 0; k < w_idx.size();) {
+    size_t e = k + 1;
+    while (e < w_idx.size() && w_idx[e] == w_idx[e - 1] + 1) ++e;
+    const int first = w_idx[k];
+    rc = cfb200_quant_sym_tensors((int32_t)(e - k), srcs + first, src_dtype, ns + first, bits, codes + first,
+                                  scale_absmax + 2 * first, 0, nullptr, stream);
+    if (rc) return rc;
+    k = e;
+  }
+  // 3. row blocks: codes from the global absmax
+  for (int i : blocks) {
+    rc = cfb200_quant_sym_apply(srcs[i], src_dtype, ns[i], bits, scale_absmax + 2 * i + 1, codes[i], scale_absmax + 2 * i, stream);
+    if (rc) return rc;
+  }
+  return CFB200_OK;
+}
+
+// ---- column-parallel GEMMs ------------------------------------------------------------------------------------------------
+extern "C" size_t cfb200_gemm_colpar_workspace_bytes(size_t M, size_t N_local, size_t K, int32_t world, int32_t w4) {
+  const size_t out_bytes = align256(M * N_local * 2);
+  size_t need = out_bytes;                                     // this rank's [M, N_local] bf16 block
+  if (world > 1 && M > 1) need += align256(out_bytes * world);  // the gathered blocks before they are interleaved
+  if (w4 && M > 16) need += align256(cfb200_gemm_w4a16_workspace_bytes(M, N_local, K));
+  return need;
+}
+
+extern "C" int32_t cfb200_gemm_w4a16_colpar(cfb200_comm* comm, const void* A, const uint8_t* w_codes, const uint16_t* w_scales,
+                                            const uint8_t* w_zps, size_t M, size_t N_local, size_t K, size_t group, void* C,
+                                            int32_t layout, void* workspace, size_t workspace_bytes, int32_t* error_flag,
+                                            void* stream) {
+  CFB_CHECK_ARG(comm != nullptr, "NULL communicator");
+  CFB_CHECK_ARG(layout == 0 || layout == 1, "layout must be 0 (row-major [M, N]) or 1 ([world][M][N_local])");
+  CFB_CHECK_ARG(N_local % 8 == 0, "N_local must be a multiple of 8 (got %zu)", N_local);
+  CFB_CHECK_ALIGNED(workspace, 256);
+  CFB_CHECK_ALIGNED(C, 16);
+  const size_t need = cfb200_gemm_colpar_workspace_bytes(M, N_local, K, comm->world, 1);
+  if (!workspace || workspace_bytes < need) return set_error(CFB200_ERR_WORKSPACE, "gemm_w4a16_colpar needs %zu bytes of workspace", need);
+  char* ws = reinterpret_cast<char*>(workspace);
+  const size_t out_bytes = align256(M * N_local * 2);
+  void* part = ws;
+  void* gathered = ws + out_bytes;
+  const bool has_gather = comm->world > 1 && M > 1;
+  void* inner = ws + out_bytes + (has_gather ? align256(out_bytes * comm->world) : 0);
+  int32_t rc;
+  if (M <= 16 && group == 128) rc = cfb200_gemv_w4a16(A, w_codes, w_scales, w_zps, M, N_local, K, group, part, 0, stream);
+  else rc = cfb200_gemm_w4a16(A, w_codes, w_scales, w_zps, M, N_local, K, group, part, 0, inner,
+                              cfb200_gemm_w4a16_workspace_bytes(M, N_local, K), error_flag, stream);
+  if (rc) return rc;
+  return gather_columns(comm, part, M, N_local, 2, C, layout, gathered, (cudaStream_t)stream);
+}
+
+extern "C" int32_t cfb200_gemm_fp8_colpar(cfb200_comm* comm, const uint8_t* A, const float* a_scales, const uint8_t* W_local,
+                                          float w_scale, size_t M, size_t N_local, size_t K, void* C, int32_t layout,
+                                          void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream) {
+  CFB_CHECK_ARG(comm != nullptr, "NULL communicator");
+  CFB_CHECK_ARG(layout == 0 || layout == 1, "layout must be 0 (row-major [M, N]) or 1 ([world][M][N_local])");
+  CFB_CHECK_ARG(N_local % 8 == 0, "N_local must be a multiple of 8 (got %zu)", N_local);
+  CFB_CHECK_ALIGNED(workspace, 256);
+  CFB_CHECK_ALIGNED(C, 16);
+  const size_t need = cfb200_gemm_colpar_workspace_bytes(M, N_local, K, comm->world, 0);
+  if (!workspace || workspace_bytes < need) return set_error(CFB200_ERR_WORKSPACE, "gemm_fp8_colpar needs %zu bytes of workspace", need);
+  char* ws = reinterpret_cast<char*>(workspace);
+  const size_t out_bytes = align256(M * N_local * 2);
+  int32_t rc = cfb200_gemm_fp8(A, a_scales, W_local, w_scale, M, N_local, K, ws, 0, error_flag, stream);
+  if (rc) return rc;
+  return gather_columns(comm, ws, M, N_local, 2, C, layout, ws + out_bytes, (cudaStream_t)stream);
+}
+
+// ---- GPTQ: token-parallel Hessian ---------------------------------------------------------------------------------------------
+extern "C" int32_t cfb200_gptq_hessian_scaled(const void* X, size_t T, size_t K, float alpha, float* H, void* xt_workspace,
+                                              size_t workspace_bytes, int32_t* error_flag, void* stream);
+
+extern "C" int32_t cfb200_gptq_hessian_sharded(cfb200_comm* comm, const void* X_local, size_t T_local, size_t T_total, size_t K,
+                                               float* H, void* xt_workspace, size_t workspace_bytes, int32_t* error_flag,
+                                               void* stream) {
+  CFB_CHECK_ARG(comm != nullptr, "NULL communicator");
+  CFB_CHECK_ARG(T_total >= T_local && T_total > 0, "T_total must cover T_local");
+  int32_t rc;
+  if (T_local > 0) rc = cfb200_gptq_hessian_scaled(X_local, T_local, K, 1.0f / (float)T_total, H, xt_workspace, workspace_bytes, error_flag, stream);
+  else rc = cudaMemsetAsync(H, 0, K * K * sizeof(float), (cudaStream_t)stream) == cudaSuccess ? CFB200_OK : set_error(CFB200_ERR_CUDA, "cudaMemsetAsync failed");
+  if (rc) return rc;
+  if (comm->world > 1) {
+    const NcclApi* api;
+    rc = nccl_api(&api);
+    if (rc) return rc;
+    CFB_NCCL(api, api->AllReduce(H, H, K * K, ncclFloat32, ncclSum, comm->nccl, (cudaStream_t)stream));
+  }
+  return CFB200_OK;
+}

@@ -990,15 +990,20 @@ extern "C" int32_t cfb200_quant_nf4(const void* src, int32_t src_dtype, size_t n
     return set_error(CFB200_ERR_WORKSPACE, "quant_nf4 needs %zu bytes of workspace, got %zu",
                      cfb200_quant_nf4_workspace_bytes(n, block), workspace_bytes);
   cudaStream_t st = (cudaStream_t)stream;
-  static thread_local int cells_ready_dev = -1;
   int dev = 0;
   CFB_CUDA(cudaGetDevice(&dev));
-  if (cells_ready_dev != dev) {
-    Nf4Cell cells[32];
-    build_nf4_cells(cells);
-    CFB_CUDA(cudaMemcpyToSymbolAsync(c_nf4_cells, cells, sizeof cells, 0, cudaMemcpyHostToDevice, st));
-    CFB_CUDA(cudaStreamSynchronize(st));  // `cells` lives on this stack frame
-    cells_ready_dev = dev;
+  if (dev < 0 || dev >= 64) return set_error(CFB200_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  {  // the code table goes to constant memory once per device (not per host thread), on the first call there
+    static std::mutex cells_mutex;
+    static bool cells_ready[64];
+    std::lock_guard<std::mutex> lock(cells_mutex);
+    if (!cells_ready[dev]) {
+      Nf4Cell cells[32];
+      build_nf4_cells(cells);
+      CFB_CUDA(cudaMemcpyToSymbolAsync(c_nf4_cells, cells, sizeof cells, 0, cudaMemcpyHostToDevice, st));
+      CFB_CUDA(cudaStreamSynchronize(st));  // `cells` lives on this stack frame
+      cells_ready[dev] = true;
+    }
   }
   float* am = reinterpret_cast<float*>(workspace);
   const bool wide = (reinterpret_cast<uintptr_t>(src) & 31) == 0;
@@ -1056,7 +1061,7 @@ extern "C" size_t cfb200_quant_nf4_static_max_elements(size_t block) { return kN
 extern "C" int32_t cfb200_quant_nf4_static(const void* src, int32_t src_dtype, size_t n, size_t block, size_t dq_block,
                                            uint8_t* codes, uint8_t* absmax8, float* absmax2, void* stream) {
   CFB_CHECK_ARG(block == 32 || block == 64 || block == 128 || block == 256, "block must be 32, 64, 128 or 256 (got %zu)", block);
-  const size_t nblocks = (n + block - 1) / block;
+  const size_t nblocks = n / block + (n % block != 0);  // no wrap-around for n near SIZE_MAX
   if (nblocks > kNf4StaticMaxBlocks)
     return set_error(CFB200_ERR_INVALID,
                      "cfb200_quant_nf4_static handles at most %zu elements at block %zu (%zu blocks of built-in scratch); got %zu "

@@ -22,6 +22,7 @@
 // NaN, infinity, a quotient beyond the code range) the vector takes the exact path: IEEE division,
 // roundf, clamp, NaN -> 0.
 #include <atomic>
+#include <mutex>
 #include <type_traits>
 #include <vector>
 
@@ -362,9 +363,12 @@ constexpr int kPConsumers = CFB_A1_CONSUMERS;  // threads that fold and quantize
 constexpr int kPThreads = kPConsumers + 32;    // + one warp that only issues the bulk copies
 constexpr int kPMaxTensors = 1024;
 constexpr int kPSlots = 8;
-constexpr int kPItemBytes = 32 * 1024;
+#ifndef CFB_A1_ITEM_KB
+#define CFB_A1_ITEM_KB 32
+#endif
+constexpr int kPItemBytes = CFB_A1_ITEM_KB * 1024;
 constexpr int kPItemVecs = kPItemBytes / 16;
-constexpr int kPBufs = 7;
+constexpr int kPBufs = 224 / CFB_A1_ITEM_KB;
 constexpr int kPSmemBytes = kPBufs * kPItemBytes;
 
 struct PSeg {
@@ -379,6 +383,22 @@ struct PSeg {
 static __device__ PSeg g_pseg[kPSlots][kPMaxTensors];
 static __device__ unsigned g_pbar[kPSlots * 32];  // one barrier counter per slot, 128 bytes apart
 static __device__ int g_pflag;                    // sticky: a bounded wait ran out
+#ifdef CFB_A1_TRACE
+// Phase time stamps (globaltimer ns) of three CTAs, for builds made with -DCFB_A1_TRACE only.
+constexpr int kTracePhases = 200, kTraceSlots = 8;
+static __device__ unsigned long long g_ptrace[3][kTracePhases][kTraceSlots];
+__device__ __forceinline__ void trace_stamp(uint32_t bid, uint32_t G, int phase, int slot) {
+  const int c = bid == 0 ? 0 : bid == G / 2 ? 1 : bid == G - 1 ? 2 : -1;
+  if (c >= 0 && phase >= 0 && phase < kTracePhases) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    g_ptrace[c][phase][slot] = t;
+  }
+}
+#define CFB_TRACE(slot) trace_stamp(bid, G, p + 1, slot)
+#else
+#define CFB_TRACE(slot) do {} while (0)
+#endif
 
 // Absmax of a stream of 16-byte vectors, one instruction per 32-bit word for each of two
 // accumulators (max.xorsign.abs takes |a|, |b| itself; the sign it leaves is dropped at the end):
@@ -425,18 +445,17 @@ struct AbsFold {
 };
 
 // All CTAs of a cooperative launch meet here.  Bounded: about a second of polling, then false.
-__device__ __forceinline__ bool grid_barrier_bounded(unsigned* ctr, unsigned target) {
+__device__ __forceinline__ bool grid_barrier_bounded(unsigned* ctr, unsigned target, unsigned sleep_ns) {
   __shared__ int s_ok;
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
-    atomicAdd(ctr, 1u);
+    asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(ctr) : "memory");  // orders this CTA's earlier atomics before the count
     int ok = 0;
     for (unsigned it = 0; it < (1u << 24); ++it) {
       unsigned v;
       asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
       if (v >= target) { ok = 1; break; }
-      __nanosleep(64);
+      if (sleep_ns) __nanosleep(sleep_ns);
     }
     s_ok = ok;
   }
@@ -523,14 +542,17 @@ __device__ __forceinline__ uint32_t items_of(const PGroup& grp, uint32_t bid, ui
 //   * the last kPBufs pass-1 items of group p+1 close the phase and stay in the ring.
 template <int DT>
 __global__ void __launch_bounds__(kPThreads, 1)
-a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float qmin, float qmax, uint32_t retain_items) {
+a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float qmin, float qmax, uint32_t retain_items,
+                  uint32_t prefetch_items, uint32_t bar_sleep_ns, uint32_t tail_first) {
   constexpr int VE = Vec16<DT>::kElems;
   constexpr int VPT = kPItemVecs / kPConsumers;  // vectors per consumer thread per item
+  static_assert(kPItemVecs % kPConsumers == 0 && VPT % 4 == 0, "the unrolled quantize loop reads four vectors per thread per trip");
   extern __shared__ __align__(128) uint8_t p_ring[];
   __shared__ __align__(8) uint64_t s_full[kPBufs], s_empty[kPBufs];
   __shared__ PGroup s_grp[3];
   __shared__ PItem s_item[kPBufs];
   __shared__ int s_fail;
+  __shared__ uint32_t s_issued;  // producer: items issued so far (read only on the failure path)
   const int tid = threadIdx.x, lane = tid & 31;
   const bool producer = tid >= kPConsumers;  // the last warp only moves data
   const uint32_t G = gridDim.x, bid = blockIdx.x;
@@ -544,6 +566,7 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     s_fail = 0;
+    s_issued = 0;
     s_grp[2].nseg = 0;  // "group -1": nothing to quantize in the first phase
     s_grp[2].end = 0;
   }
@@ -558,23 +581,29 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
   unsigned nbar = 0;
   const uint64_t pol_first = l2_policy_evict_first();
 
+  // item k of this CTA in group grp: its tensor, chunk, address and length
+  auto locate = [&](const PGroup& grp, uint32_t k, int& sidx, uint32_t& ch, uint32_t& bytes) -> const uint8_t* {
+    const uint32_t g = bid + k * G;
+    sidx = 0;
+    while (sidx + 1 < grp.nseg && grp.first_chunk[sidx + 1] <= g) ++sidx;
+    ch = g - grp.first_chunk[sidx];
+    const size_t left = grp.nvec[sidx] * 16 - (size_t)ch * kPItemBytes;
+    bytes = (uint32_t)(left < (size_t)kPItemBytes ? left : (size_t)kPItemBytes);
+    return grp.src[sidx] + (size_t)ch * kPItemBytes;
+  };
   // producer lane 0: item k of this CTA in group grp -> ring buffer seq % kPBufs
   auto issue = [&](const PGroup& grp, uint32_t k, uint32_t kind, bool evict_first) -> bool {
     const int b = (int)(seq % kPBufs);
-    ++seq;
     if (used & (1u << b)) {
       if (!mbar_wait_bounded(empty0 + 8 * b, (empty_par >> b) & 1u)) return false;
       empty_par ^= 1u << b;
     }
+    ++seq;
     used |= 1u << b;
-    const uint32_t g = bid + k * G;
-    int sidx = 0;
-    while (sidx + 1 < grp.nseg && grp.first_chunk[sidx + 1] <= g) ++sidx;
-    const uint32_t ch = g - grp.first_chunk[sidx];
-    const size_t left = grp.nvec[sidx] * 16 - (size_t)ch * kPItemBytes;
-    const uint32_t bytes = (uint32_t)(left < (size_t)kPItemBytes ? left : (size_t)kPItemBytes);
+    int sidx;
+    uint32_t ch, bytes;
+    const uint8_t* src = locate(grp, k, sidx, ch, bytes);
     s_item[b] = PItem{(uint32_t)sidx, ch, bytes / 16, kind};
-    const uint8_t* src = grp.src[sidx] + (size_t)ch * kPItemBytes;
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(full0 + 8 * b), "r"(bytes) : "memory");
     if (evict_first)
       asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
@@ -624,19 +653,50 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
       if (lane == 0) {
         bool ok = true;
         uint32_t a = 0, b2 = 0;
+        CFB_TRACE(5);
+        // Reload order: the last `retain_items` reloads are the lines pass 1 left in L2 at normal priority.  They go
+        // first (oldest of them first), while L2 still holds them; the lines that were let go follow.
+        const uint32_t Rk = tail_first ? (retain_items < A ? retain_items : A) : A;
         while (ok && (a < A || b2 < Bfree)) {  // proportional interleave
-          if (a < A && (b2 >= Bfree || (uint64_t)a * Bfree <= (uint64_t)b2 * A)) ok = issue(cur, a++, 1u, true);
+          if (a < A && (b2 >= Bfree || (uint64_t)a * Bfree <= (uint64_t)b2 * A)) {
+            ok = issue(cur, a < Rk ? A - Rk + a : a - Rk, 1u, true);
+            ++a;
+          }
           else {  // early items would be gone from L2 before their second read anyway: let them go first
             const bool early = b2 + retain_items < Bfree;
             ok = issue(nxt, b2++, 0u, early);
           }
         }
         for (; ok && b2 < Tn; ++b2) ok = issue(nxt, b2, 2u, true);  // the items that stay
+        s_issued = seq;
+        CFB_TRACE(6);
         if (!ok) s_fail = 1;
       }
       __syncwarp();
       // the group after next, for the following phase (its slot held group p - 1, which is done)
-      setup_group<VE>(s_grp[(p + 2) % 3], segs, count, nxt.nseg ? nxt.end : count, lane);
+      PGroup& nn = s_grp[(p + 2) % 3];
+      setup_group<VE>(nn, segs, count, nxt.nseg ? nxt.end : count, lane);
+      // Every ring buffer now holds (or is about to receive) an item that stays until the scale of the next group is
+      // known, so no copy into shared memory can be issued before the grid barrier.  L2 needs no buffer: the first
+      // items of the next phase (reloads of the next group, first lines of the group after it) are requested into L2
+      // now, which keeps HBM busy across the barrier; the copies issued after it find them there.
+      if (lane == 0 && prefetch_items != 0 && nxt.nseg != 0) {
+        const uint32_t Tc2 = Tn, Tn2 = items_of(nn, bid, G);
+        const uint32_t A2 = Tc2 > (uint32_t)kPBufs ? Tc2 - kPBufs : 0;
+        const uint32_t B2 = Tn2, Bf2 = Tn2 > (uint32_t)kPBufs ? Tn2 - kPBufs : 0;
+        const uint32_t Rk2 = tail_first ? (retain_items < A2 ? retain_items : A2) : A2;
+        uint32_t a = 0, b2 = 0;
+        for (uint32_t i = 0; i < prefetch_items && (a < A2 || b2 < B2); ++i) {  // the order the next phase issues them in
+          int sidx;
+          uint32_t ch, bytes;
+          const uint8_t* src;
+          if (a < A2 && (b2 >= Bf2 || (uint64_t)a * Bf2 <= (uint64_t)b2 * A2)) {
+            src = locate(nxt, a < Rk2 ? A2 - Rk2 + a : a - Rk2, sidx, ch, bytes);
+            ++a;
+          } else src = locate(nn, b2++, sidx, ch, bytes);
+          if (bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+        }
+      }
     } else {
       // tails of both groups: elements past the last whole vector (CTA 0)
       if (bid == 0) {
@@ -658,12 +718,14 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
         }
       }
       bool ok = true;
+      if (tid == 0) CFB_TRACE(0);
       // 1. what pass 1 left in the ring, oldest first
       for (uint32_t r = 0; r < Rc; ++r) {
         const int b = (int)((seq - Rc + r) % kPBufs);
         quantize_item(cur, b);
         release(b);
       }
+      if (tid == 0) CFB_TRACE(1);
       // 2. the merged stream
       AbsFold<DT> f;
       int fseg = -1;
@@ -679,8 +741,8 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
       const uint32_t n_items = A + Tn;
       for (uint32_t j = 0; j < n_items; ++j) {
         const int b = (int)(seq % kPBufs);
-        ++seq;
         if (!mbar_wait_bounded(full0 + 8 * b, (full_par >> b) & 1u)) { ok = false; break; }
+        ++seq;
         full_par ^= 1u << b;
         const uint32_t kind = s_item[b].kind;
         if (kind & 1u) {
@@ -699,12 +761,23 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
           if (!(kind & 2u)) release(b);
         }
       }
+      if (tid == 0) CFB_TRACE(2);
       flush();
       if (!ok) s_fail = 1;
     }
     __syncthreads();
     if (s_fail) {
-      if (tid == 0) g_pflag = 1;
+      // A bounded wait ran out.  Copies already issued still write into this CTA's shared memory: wait (bounded
+      // again) for each of them before the CTA returns, then report through the sticky device flag.
+      if (tid == 0) {
+        g_pflag = 1;
+        for (uint32_t j = seq; j < s_issued; ++j) {
+          const int b = (int)(j % kPBufs);
+          if (!mbar_wait_bounded(full0 + 8 * b, (full_par >> b) & 1u)) break;
+          full_par ^= 1u << b;
+        }
+      }
+      __syncthreads();
       return;
     }
     if (bid == 0 && tid < cur.nseg) cur.scale_absmax[tid][0] = cur.scale[tid];  // group p is done: publish its scale
@@ -715,7 +788,8 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
       if (nxt.odd[tid] != 0u) atomicOr(reinterpret_cast<unsigned*>(nxt.scale_absmax[tid]), 1u);
     }
     ++nbar;
-    if (!grid_barrier_bounded(bar, nbar * G)) {
+    if (tid == 0) CFB_TRACE(3);
+    if (!grid_barrier_bounded(bar, nbar * G, bar_sleep_ns)) {
       if (tid == 0) g_pflag = 1;
       return;
     }
@@ -729,6 +803,7 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
       nxt.inv[tid] = __fdiv_rn(1.0f, scale);
       nxt.odd[tid] = obits;
     }
+    if (tid == 0) CFB_TRACE(4);
     __syncthreads();
   }
 }
@@ -825,7 +900,11 @@ int32_t launch_persist_dt(const PSeg* table, int count, unsigned* bar, float qmi
   }
   const long long retain_mb = tunable(kTuneA1RetainMB);
   uint32_t retain_items = retain_mb >= 0 ? (uint32_t)(((size_t)retain_mb << 20) / ((size_t)kPItemBytes * sm_count())) : 0xffffffffu / 2;
-  void* args[] = {(void*)&table, (void*)&count, (void*)&bar, (void*)&qmin, (void*)&qmax, (void*)&retain_items};
+  long long pf = tunable(kTuneA1Prefetch), bs = tunable(kTuneA1BarSleep);
+  uint32_t prefetch_items = (uint32_t)(pf < 0 ? 0 : pf > 64 ? 64 : pf), bar_sleep_ns = (uint32_t)(bs < 0 ? 0 : bs > 1000 ? 1000 : bs);
+  uint32_t tail_first = tunable(kTuneA1TailFirst) != 0;
+  void* args[] = {(void*)&table, (void*)&count, (void*)&bar, (void*)&qmin, (void*)&qmax, (void*)&retain_items,
+                  (void*)&prefetch_items, (void*)&bar_sleep_ns, (void*)&tail_first};
   CFB_CUDA(cudaLaunchCooperativeKernel((const void*)a1_persist_kernel<DT>, dim3((unsigned)sm_count()), dim3(kPThreads), args,
                                        (size_t)kPSmemBytes, st));
   return CFB200_OK;
@@ -835,8 +914,16 @@ int32_t launch_persist_dt(const PSeg* table, int count, unsigned* bar, float qmi
 int32_t run_persist(int32_t count, const void* const* srcs, int32_t dt, const size_t* ns, float qmin, float qmax,
                     int8_t* const* codes, float* scale_absmax, const int* group_end, int ng, size_t budget, void* const* stage_events,
                     cudaStream_t st) {
-  static std::atomic<unsigned> next_slot{0};
+  // Descriptor tables and barrier words are handed out round-robin, per device.  A slot is reused only after the launch
+  // that last read it has finished (an event per slot, waited for on the host), so any number of calls may be in
+  // flight on any streams and host threads.
+  static std::mutex slot_mutex;
+  static unsigned next_slot[64];
+  static cudaEvent_t slot_done[64][kPSlots];
   int launch = 0;
+  int dev = 0;
+  CFB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(CFB200_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
   PSeg* dev_table = nullptr;
   unsigned* dev_bar = nullptr;
   CFB_CUDA(cudaGetSymbolAddress((void**)&dev_table, g_pseg));
@@ -859,7 +946,10 @@ int32_t run_persist(int32_t count, const void* const* srcs, int32_t dt, const si
         host.push_back(sg);
       }
     }
-    const unsigned slot = next_slot.fetch_add(1) % kPSlots;
+    std::lock_guard<std::mutex> lock(slot_mutex);
+    const unsigned slot = next_slot[dev]++ % kPSlots;
+    if (!slot_done[dev][slot]) CFB_CUDA(cudaEventCreateWithFlags(&slot_done[dev][slot], cudaEventDisableTiming));
+    else CFB_CUDA(cudaEventSynchronize(slot_done[dev][slot]));
     PSeg* table = dev_table + (size_t)slot * kPMaxTensors;
     unsigned* bar = dev_bar + (size_t)slot * 32;
     CFB_CUDA(cudaMemcpyAsync(table, host.data(), host.size() * sizeof(PSeg), cudaMemcpyHostToDevice, st));
@@ -874,6 +964,7 @@ int32_t run_persist(int32_t count, const void* const* srcs, int32_t dt, const si
       default: rc = launch_persist_dt<CFB200_BF16>(table, n, bar, qmin, qmax, st); break;
     }
     if (rc) return rc;
+    CFB_CUDA(cudaEventRecord(slot_done[dev][slot], st));
     g = g_hi;
   }
   if (stage_events && stage_events[launch]) CFB_CUDA(cudaEventRecord((cudaEvent_t)stage_events[launch], st));
@@ -884,6 +975,24 @@ int32_t run_persist(int32_t count, const void* const* srcs, int32_t dt, const si
 }  // namespace cfb
 
 using namespace cfb;
+
+// 0 = no bounded wait of the persistent kernel has run out on the current device (sticky); synchronises the device.
+extern "C" int32_t cfb200_quant_sym_status(int32_t* flag_host) {
+  CFB_CHECK_ARG(flag_host != nullptr, "NULL argument");
+  CFB_CUDA(cudaDeviceSynchronize());
+  int v = 0;
+  CFB_CUDA(cudaMemcpyFromSymbol(&v, g_pflag, sizeof(int)));
+  *flag_host = v;
+  return CFB200_OK;
+}
+
+#ifdef CFB_A1_TRACE
+extern "C" int32_t cfb200_debug_a1_trace(unsigned long long* host_out /* 3 * 200 * 8 */) {
+  CFB_CUDA(cudaDeviceSynchronize());
+  CFB_CUDA(cudaMemcpyFromSymbol(host_out, g_ptrace, sizeof(unsigned long long) * 3 * kTracePhases * kTraceSlots));
+  return CFB200_OK;
+}
+#endif
 
 extern "C" int32_t cfb200_quant_sym_apply(const void* src, int32_t src_dtype, size_t n, int32_t bits,
                                           const float* absmax, int8_t* codes, float* scale_absmax, void* stream) {

@@ -16,14 +16,25 @@ import torch
 import torch.distributed as dist
 
 
-def assign_tensors(sizes: Sequence[int], world: int) -> list[int]:
+def assign_tensors(sizes: Sequence[int], world: int, split_min_bytes: int = 0) -> list[int]:
     """Owner rank of each tensor: largest first onto the least-loaded rank (ties -> lowest rank,
-    equal sizes keep their order), computed identically on every rank, so nothing is exchanged."""
+    equal sizes keep their order), computed identically on every rank, so nothing is exchanged.
+    With split_min_bytes > 0 and more than one rank, a tensor of that many bytes or more is marked -1: it is cut into
+    row blocks and every rank takes one (its bytes count 1/world towards every rank's load).  This is the rule of
+    cfb200_shard_assign, restated for the tests."""
     if world < 1:
         raise ValueError("world must be >= 1")
-    order = sorted(range(len(sizes)), key=lambda i: (-int(sizes[i]), i))
     load = [0] * world
     owner = [0] * len(sizes)
+    whole = []
+    for i, b in enumerate(sizes):
+        if world > 1 and split_min_bytes > 0 and int(b) >= split_min_bytes:
+            owner[i] = -1
+            for r in range(world):
+                load[r] += int(b) // world
+        else:
+            whole.append(i)
+    order = sorted(whole, key=lambda i: (-int(sizes[i]), i))
     for i in order:
         r = min(range(world), key=lambda k: (load[k], k))
         owner[i] = r

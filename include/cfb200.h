@@ -49,8 +49,10 @@ const char* cfb200_version(void);
 /* Performance knob (process-wide, never changes results).  Keys: "a1_persist" (1, default: f16 / bf16
  * lists and large tensors run as one cooperative launch; 2: f32 too; 0: one launch per tensor group), "a1_group_mb"
  * (L2 budget of a tensor group, default 64), "a1_retain_mb" (MB of a group's tail that the first
- * pass leaves in L2 at normal priority, default 40; negative = everything), "a1_keep_mb",
- * "a1_demote", "a1_merge" (variants of the launch-per-group path), "gemv_ring" (1, default: decode
+ * pass leaves in L2 at normal priority, default 60; negative = everything), "a1_tail_first" (1, default: the quantize
+ * pass re-reads that tail before the lines that were let go; 0: oldest lines first), "a1_keep_mb",
+ * "a1_demote", "a1_merge" (variants of the launch-per-group path), "a1_prefetch" (32 KB items per CTA that the cooperative
+ * launch requests into L2 ahead of each grid barrier, default 0 = none), "a1_bar_sleep" (ns between polls of that barrier, default 0), "gemv_ring" (1, default: decode
  * shapes with 16 MB of packed weights or more use the shared-memory ring kernel; 0: never; n > 1: from n MB), "gemv_ring_rounds", "w4_split_k" (W4A16 prefill
  * with M <= 256: 0 = automatic split-K, 1 = never, n = at most n slices; changes the summation
  * order of the f32 accumulation and nothing else). */
@@ -81,8 +83,8 @@ int32_t cfb200_quant_sym_apply(const void* src, int32_t src_dtype, size_t n, int
  * overlapped with the absmax pass of the next); for f32 sources, or with cfb200_tune("a1_persist", 0),
  * the two passes of successive groups share launches, groups + 1 in total.  The _plan call returns the number of
  * launches as n_stages.  The default mode copies a descriptor table from host memory, so it must
- * not be called while `stream` is being captured into a CUDA graph; at most 8 calls may be in
- * flight on one device at a time.
+ * not be called while `stream` is being captured into a CUDA graph.  Calls may come from several host threads and
+ * streams: the eight descriptor slots of a device are recycled as their launches finish (the call blocks until one is free).
  * stage_events: NULL, or n_stages + 1 cudaEvent_t handles; handle k is recorded before launch k
  * and the last one after the final launch (for per-launch timing on `stream`). */
 int32_t cfb200_quant_sym_tensors_plan(int32_t count, const size_t* ns, int32_t src_dtype,
@@ -91,6 +93,13 @@ int32_t cfb200_quant_sym_tensors(int32_t count, const void* const* srcs, int32_t
                                  const size_t* ns, int32_t bits, int8_t* const* codes,
                                  float* scale_absmax, size_t l2_group_bytes,
                                  void* const* stage_events, void* stream);
+
+/* The cooperative launch above bounds every wait it makes (its bulk copies, its grid barrier).  If one runs out, the
+ * CTAs stop, wait for the copies they still have in flight and return, and the codes and scales of that call are
+ * incomplete although the call itself returned 0.  This call synchronises the current device and reports whether
+ * that has ever happened on it (0 = never; sticky until the process ends).  cfb200_store_run_pipeline checks it
+ * before it reports success.  (No counterpart in the reference: its pass cannot fail half-way.) */
+int32_t cfb200_quant_sym_status(int32_t* flag_host);
 
 /* ---- A6: per-tensor fake quantization (QAT-STE) --------------------------------------------
  * Replaces run_qat_ste's arithmetic (src/passes/quantize/formats.rs:764-769): f32 in, f32 out,
@@ -288,6 +297,71 @@ int32_t cfb200_gptq_quantize(const void* W, int32_t w_dtype, size_t N, size_t K,
                              uint8_t* codes, uint16_t* scales, uint8_t* zero_points,
                              float* w_dequant, void* workspace, size_t workspace_bytes,
                              void* stream);
+
+/* H = alpha * X^T X (cfb200_gptq_hessian is this with alpha = 1 / T): one token shard's share of a Hessian that
+ * several ranks accumulate, alpha = 1 / total tokens. */
+int32_t cfb200_gptq_hessian_scaled(const void* X, size_t T, size_t K, float alpha, float* H, void* xt_workspace,
+                                   size_t workspace_bytes, int32_t* error_flag, void* stream);
+
+/* ---- Several GPUs of one machine ------------------------------------------------------------------
+ * One communicator per GPU: one process per GPU (cfb200_comm_unique_id on one rank, the 128 bytes handed to the others
+ * by whatever the host has -- MPI, a file, torch.distributed --, cfb200_comm_init on every rank with its device
+ * current), or one process that drives `ndev` devices from one host thread per device (cfb200_comm_init_local).
+ * Communication is plain NCCL (opened with dlopen when the first of these calls is made; the rest of the library works
+ * without it), collectives are enqueued on the caller's stream, no kernel reads another GPU's memory.
+ * The reference has no counterpart: it stamps all_gather / all_reduce attributes on its graph
+ * (src/passes/distributed/spmd.rs:416-478) and evaluates them as the identity (src/codegen/eval.rs:1449-1455).
+ *
+ * Placement (host arithmetic, the same answer on every rank, nothing exchanged):
+ *  cfb200_shard_assign: owner[i] = rank that quantizes tensor i whole -- largest first onto the least-loaded rank, equal
+ *    sizes in store order, ties to the lowest rank -- or -1 for a tensor of split_min_bytes or more (0 = never), which
+ *    every rank takes a row block of.
+ *  cfb200_shard_row_range: rows [begin, end) of `rank` when `rows` rows are dealt out in units of `align` rows; blocks
+ *    differ by at most one unit, trailing ranks may be empty.
+ *
+ * cfb200_quant_sym_tensors_sharded: A1 over this rank's part of a store (QuantizeWeightsPass::run's loop,
+ *  src/passes/quantize/schemes.rs:324-452, dealt over ranks).  Arguments as cfb200_quant_sym_tensors; is_row_block[i] != 0
+ *  marks a buffer that holds this rank's rows of a tensor split over ALL ranks (every rank passes the split tensors in
+ *  the same order; an empty block has ns[i] == 0).  Whole tensors need nothing from other ranks; for a row block the
+ *  ranks take the maximum of their partial absmax (one float per split tensor, one grouped ncclAllReduce), so scale and
+ *  codes are bit-identical to the one-GPU result.  scale_absmax[2 i] holds the tensor's scale on every rank.
+ *
+ * Column-parallel GEMMs: every rank holds N_local = N / world rows of the [N, K] weight (rank r: rows
+ *  [r N_local, (r + 1) N_local), with their scales and zero points) and the whole activation matrix.  The rank's block of
+ *  the product comes from cfb200_gemm_w4a16 (cfb200_gemv_w4a16 when M <= 16 and group == 128) or cfb200_gemm_fp8; one
+ *  ncclAllGather then leaves the whole bf16 product in C on every rank: layout 0 = row-major [M, N] (the gathered
+ *  blocks are interleaved by one more launch when M > 1), layout 1 = [world][M][N_local] as gathered.
+ *  N_local % 8 == 0; workspace (256-byte aligned) of cfb200_gemm_colpar_workspace_bytes(..., w4 = 1 or 0).
+ *
+ * cfb200_gptq_hessian_sharded: every rank passes its T_local calibration tokens (T_local % 8 == 0, may be 0); H receives
+ *  X^T X / T_total summed over ranks (one ncclAllReduce of K x K floats).  The factor U is then computed on every rank
+ *  (cfb200_gptq_prepare) and each rank walks its own output rows with cfb200_gptq_quantize: no communication in the
+ *  walk.  The sum over ranks adds in another order than one GPU does, so H agrees to rounding, not bit for bit; pass
+ *  every token to every rank (T_local = T_total, world-size-1 behaviour) when bit-identical codes are wanted. */
+typedef struct cfb200_comm cfb200_comm_t;
+int32_t cfb200_comm_unique_id(void* id_out_128_host);
+int32_t cfb200_comm_init(const void* id_128_host, int32_t world, int32_t rank, cfb200_comm_t** comm_out);
+int32_t cfb200_comm_init_local(int32_t ndev, const int32_t* devices, cfb200_comm_t** comms_out);
+int32_t cfb200_comm_world(const cfb200_comm_t* comm);
+int32_t cfb200_comm_rank(const cfb200_comm_t* comm);
+void cfb200_comm_free(cfb200_comm_t* comm);
+int32_t cfb200_nccl_version(int32_t* version_out);
+int32_t cfb200_shard_assign(int32_t count, const size_t* nbytes, int32_t world, size_t split_min_bytes, int32_t* owner);
+int32_t cfb200_shard_row_range(size_t rows, int32_t world, int32_t rank, size_t align, size_t* row_begin, size_t* row_end);
+int32_t cfb200_quant_sym_tensors_sharded(cfb200_comm_t* comm, int32_t count, const void* const* srcs, int32_t src_dtype,
+                                         const size_t* ns, const int32_t* is_row_block, int32_t bits,
+                                         int8_t* const* codes, float* scale_absmax, void* stream);
+size_t cfb200_gemm_colpar_workspace_bytes(size_t M, size_t N_local, size_t K, int32_t world, int32_t w4);
+int32_t cfb200_gemm_w4a16_colpar(cfb200_comm_t* comm, const void* A, const uint8_t* w_codes, const uint16_t* w_scales,
+                                 const uint8_t* w_zps, size_t M, size_t N_local, size_t K, size_t group, void* C,
+                                 int32_t layout, void* workspace, size_t workspace_bytes, int32_t* error_flag,
+                                 void* stream);
+int32_t cfb200_gemm_fp8_colpar(cfb200_comm_t* comm, const uint8_t* A, const float* a_scales, const uint8_t* W_local,
+                               float w_scale, size_t M, size_t N_local, size_t K, void* C, int32_t layout,
+                               void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream);
+int32_t cfb200_gptq_hessian_sharded(cfb200_comm_t* comm, const void* X_local, size_t T_local, size_t T_total, size_t K,
+                                    float* H, void* xt_workspace, size_t workspace_bytes, int32_t* error_flag,
+                                    void* stream);
 
 /* ---- GGUF block formats (the on-disk step after quantize) ----------------------------------------
  * cfb200_gguf_pack_q8_0: what export_gguf_bytes does with a per-tensor INT8 tensor
