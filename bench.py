@@ -10,8 +10,12 @@ GB/s counts ALGORITHMIC bytes: 2 B read + 1 B written per element.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-N > 1 is launched with torch.distributed.run (one rank per GPU); every rank quantizes one set's
-worth of tensors (weak scaling, no data-path collective), times are max over ranks.
+N > 1 is launched with torch.distributed.run (one rank per GPU).  `value` is weak scaling: every rank quantizes one
+set's worth of tensors, no data-path collective, times are max over ranks.  The same line carries `strong`: ONE set
+dealt over the N ranks (whole tensors largest first, the two vocabulary tensors cut into row blocks whose partial absmax
+meet in one NCCL MAX all-reduce of one float each), `nf4_llama2_7b` (BASELINE config 3: one Llama-2-7B-shaped set dealt
+per tensor over the ranks) and, for N > 1, `colpar` (column-parallel W4A16 / FP8 GEMM + NCCL all-gather).  At N = 1 the
+`secondary` block times the GEMM / decode / GPTQ figures of BASELINE configs 2, 4 and 5.
 `--impl reference` times the CPU restatement of the reference pass (the reference is Rust and
 cannot be built here) on the host cores over a bounded sample of the same workload.
 """
@@ -30,6 +34,7 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+WORKLOAD = "llama3-8b-shaped bf16 weight set (8.03e9 elements per GPU), quantize(bits=8) per-tensor symmetric INT8"
 METRIC = "weight_quantize_throughput"
 UNIT = "GB/s"
 ALG_BYTES_PER_ELEM = 3.0  # bf16 read once + int8 written (the second read is an implementation cost)
@@ -160,13 +165,60 @@ def run_reference(args):
     cb["value"] = val
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "llama3-8b-shaped bf16 weight set, quantize(bits=8) per-tensor symmetric INT8",
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD,
                        "reference_impl": "C++ restatement of the reference's Rust CPU pass (Rust toolchain absent), all host threads",
                        "step": cb["sample"]},
             "cpu_baseline": cb,
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
+
+
+def llama2_7b_tensors() -> list[tuple[str, int, int]]:
+    t = []
+    for layer in range(32):
+        for name, r, c in (("q", 4096, 4096), ("k", 4096, 4096), ("v", 4096, 4096), ("o", 4096, 4096),
+                           ("gate", 11008, 4096), ("up", 11008, 4096), ("down", 4096, 11008)):
+            t.append((f"layers.{layer}.{name}", r, c))
+    t.append(("embed_tokens", 32000, 4096))
+    t.append(("lm_head", 32000, 4096))
+    return t
+
+
+def traffic_ratios():
+    """DRAM bytes per algorithmic byte of the persistent A1 kernel, read from the ncu summary that sits under profiles/
+    (lines `traffic_ratio_layers: x` / `traffic_ratio_vocab: x`); None when the summary is absent."""
+    import re
+    f = ROOT / "profiles" / "a1_persist_kernel_llama3-8b_layers.md"
+    try:
+        text = f.read_text()
+        lay = float(re.search(r"traffic_ratio_layers:\s*([0-9.]+)", text).group(1))
+        voc = float(re.search(r"traffic_ratio_vocab:\s*([0-9.]+)", text).group(1))
+        return lay, voc
+    except Exception:
+        return None
+
+
+def timed_steps(step, steps, stream, barrier, world, dev):
+    """K steps between two events on `stream`, barrier + synchronize on both sides, max over ranks.  Returns ms per step
+    and every rank's own ms per step."""
+    import torch
+    import torch.distributed as dist
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record(stream)
+    for _ in range(steps):
+        step()
+    t1.record(stream)
+    barrier()
+    ms = t0.elapsed_time(t1) / steps
+    per_rank = [ms]
+    if world > 1:
+        tt = torch.tensor([ms], device=dev)
+        gathered = [torch.zeros_like(tt) for _ in range(world)]
+        dist.all_gather(gathered, tt)
+        per_rank = [float(x.item()) for x in gathered]
+    return max(per_rank), per_rank
 
 
 def main():
@@ -177,9 +229,11 @@ def main():
     ap.add_argument("--impl", default="castforge_b200")
     ap.add_argument("--layers", type=int, default=32, help="decoder layers of the set (32 = full workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-secondary", action="store_true", help="skip the GEMM / decode figures reported beside the headline metric")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the GEMM / decode / GPTQ figures reported beside the headline metric")
+    ap.add_argument("--no-strong", action="store_true", help="skip the one-set-over-N-ranks and column-parallel legs")
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="performance knob passed to cfb200_tune (never changes results)")
-    ap.add_argument("--e2e-layers", type=int, default=4, help="decoder layers streamed from host per e2e step")
+    ap.add_argument("--e2e-layers", type=int, default=-1,
+                    help="decoder layers streamed from host per e2e step (-1: the whole set at one GPU when host memory allows, else 4)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -204,9 +258,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local_rank}"))
     torch.cuda.set_device(local_rank)
     dev = torch.device(f"cuda:{local_rank}")
-    from castforge_b200 import sharding
+    from castforge_b200 import multi_gpu, sharding
     all_cpus = os.sched_getaffinity(0)
     numa_cpus = sharding.bind_host_to_device_node(local_rank)  # host staging memory local to this GPU's PCIe root
+    comm = multi_gpu.Comm.from_torch_distributed() if world > 1 else None   # the library's own NCCL communicator
 
     tensors = llama3_8b_tensors()
     if args.layers != 32:
@@ -275,6 +330,12 @@ def main():
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         ms_total = float(tt.item())
     ms_step = ms_total / args.steps
+    # the cooperative kernel reports an expired wait through a device flag, not a return code: a run that saw one
+    # has no valid figure
+    a1_flag = ctypes.c_int32(-1)
+    check(lib.cfb200_quant_sym_status(ctypes.byref(a1_flag)))
+    if a1_flag.value != 0:
+        raise SystemExit("bench: the A1 kernel gave up a bounded wait on this device; its outputs are incomplete")
     # dominant kernel.  Default: a1_persist_kernel<bf16>, ONE cooperative launch per step that walks the
     # whole list (per tensor group: absmax pass, grid barrier, quantize pass).  With --tune a1_persist=0:
     # a1_stage_kernel<bf16>, one launch per tensor group.  Algorithmic bytes = 2 B read + 1 B written per
@@ -285,16 +346,17 @@ def main():
     k_alg_bytes = n_total * ALG_BYTES_PER_ELEM / n_stages   # average algorithmic bytes per launch
     achieved = k_alg_bytes / (k_avg_ms * 1e-3) / 1e9
     peak, peak_src = measured_peak_hbm()
+    traffic, traffic_src = None, "no ncu summary of this kernel under profiles/"
     if persist:
         kernel_name = "a1_persist_kernel<bf16> (whole list in one cooperative launch: absmax pass, grid barrier, quantize pass per tensor group)"
-        big = sum(r * c for (_, r, c) in mine if r * c * 2 > (512 << 20))   # tensors far beyond L2 + shared memory
-        traffic_ratio = (1.216 * (n_total - big) + 1.597 * big) / n_total
-        traffic_src = ("ncu dram__bytes_read+write of smaller captures scaled by elements: 1.216 x algorithmic for decoder-layer tensors "
-                       "(profiles/a1_persist_kernel_llama3-8b_layers.md), 1.597 x for the 128256x4096 tensors")
+        tr = traffic_ratios()
+        if tr:
+            big = sum(r * c for (_, r, c) in mine if r * c * 2 > (512 << 20))   # tensors far beyond L2 + shared memory
+            traffic = (tr[0] * (n_total - big) + tr[1] * big) / n_total * k_alg_bytes
+            traffic_src = (f"ncu dram__bytes_read+write of smaller captures of the same kernel, scaled by elements: {tr[0]} x algorithmic "
+                           f"for decoder-layer tensors, {tr[1]} x for the 128256x4096 tensors")
     else:
         kernel_name = "a1_stage_kernel<bf16> (pass 2 of one tensor group + pass 1 of the next)"
-        traffic_ratio = 1.27
-        traffic_src = "ncu small-case capture scaled by units (profiles/a1_stage_kernel_llama3-8b_layer.md)"
 
     # ---- e2e: host buffers in, codes + scales back to the host, copies inside the timed region ---
     e2e = run_e2e(args, lib, dev, rank, world, mine)
@@ -306,23 +368,38 @@ def main():
         total_elems_all = float(tt.item())
     value = total_elems_all * ALG_BYTES_PER_ELEM / (ms_step * 1e-3) / 1e9
 
+    spot = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        # one tensor of the timed run against the CPU restatement (the checker of the CPU-baseline leg): k of layer 0
+        i_k = next(i for i, (n, _, _) in enumerate(mine) if n.endswith("layers.0.k"))
+        off, (_, r, c) = offs[i_k], mine[i_k]
+        spot = (arena[off: off + r * c].view(torch.int16).cpu().numpy().view("uint16"), codes[off: off + r * c].cpu().numpy(),
+                float(scales[2 * i_k].item()))
+
+    extra = {}
+    if not args.no_strong:
+        extra["strong"] = strong_leg(args, lib, comm, dev, rank, world, arena, codes, tensors, barrier, stream)
+        extra["nf4_llama2_7b"] = nf4_leg(args, lib, dev, rank, world, arena, codes, barrier, stream)
+        if world > 1:
+            extra["colpar"] = colpar_leg(args, comm, dev, rank, world, barrier, stream)
+
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
                 "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-                "dtype": "f32", "data": "synthetic",
-                "config": {"workload": "llama3-8b-shaped bf16 weight set (8.03e9 elements per GPU), quantize(bits=8) per-tensor symmetric INT8",
+                "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": WORKLOAD,
                            "tensors_per_gpu": len(views), "elements_per_gpu": n_total,
                            "bytes_counted": "2 B read + 1 B written per element (algorithmic)",
                            "l2": "inputs (16 GB per GPU) are larger than L2; no flush needed"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": n_stages * args.steps,
                 "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved,
                              "peak": peak, "peak_source": peak_src, "unit": "GB/s", "frac": achieved / peak,
-                             # DRAM bytes per launch from ncu captures of smaller cases of the same kernel (three decoder
-                             # layers: 1.216 x algorithmic; one 128256x4096 tensor: 1.597 x), weighted by the bytes of
-                             # each kind in this rank's list; traffic grows in proportion to the elements processed.
-                             "traffic": traffic_ratio * k_alg_bytes, "traffic_source": traffic_src,
+                             "traffic": traffic, "traffic_source": traffic_src,
                              "launches": k_launches, "avg_ms": k_avg_ms,
                              "whole_step_frac": value / world / peak}}
+        line.update(extra)
+        del arena, codes
+        torch.cuda.empty_cache()
         if not args.no_secondary and world == 1:
             line["secondary"] = secondary_metrics(dev)
         line["e2e"]["host_cpus_bound_to_gpu_numa_node"] = len(numa_cpus) if numa_cpus else None
@@ -331,11 +408,167 @@ def main():
             cb, _ = cpu_baseline_run(0, 12.0)
             cb1, _ = cpu_baseline_run(1, 8.0)
             cb["single_thread_value"] = cb1["value"]
+            if spot is not None:
+                import numpy as np
+                import oracle_lib
+                orc = oracle_lib.load()
+                q, sc, _ = orc.quant_sym(orc.to_f32(spot[0], 2, threads=0), 8, threads=0)
+                if not (np.array_equal(q, spot[1]) and float(sc) == spot[2]):
+                    raise SystemExit("bench: codes / scale of the timed run differ from the CPU restatement on layers.0.k")
+                cb["spot_check"] = "layers.0.k of the timed GPU run == the CPU restatement (codes and scale)"
             line["cpu_baseline"] = cb
         print(json.dumps(line))
+    if comm is not None:
+        comm.close()
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def strong_leg(args, lib, comm, dev, rank, world, arena, codes, tensors, barrier, stream):
+    """ONE 8B-shaped set over the N ranks: cfb200_shard_assign deals whole tensors (largest first) and marks the
+    two 128256 x 4096 tensors for row blocks; every rank runs cfb200_quant_sym_tensors_sharded on its part (the row
+    blocks' partial absmax meet in one grouped NCCL MAX all-reduce of one float each).  At N = 1 this is the weak leg."""
+    import torch
+    import torch.distributed as dist
+    from castforge_b200 import multi_gpu
+    from castforge_b200._lib import check
+    vp = ctypes.c_void_p
+    nbytes = [r * c * 2 for _, r, c in tensors]
+    owner = multi_gpu.shard_assign(nbytes, world, 512 << 20)
+    parts = []  # (elements, is_row_block)
+    for (name, r, c), ow in zip(tensors, owner):
+        if ow == -1:
+            lo, hi = multi_gpu.shard_row_range(r, world, rank, 1)
+            parts.append(((hi - lo) * c, 1))
+        elif ow == rank:
+            parts.append((r * c, 0))
+    offs, o = [], 0
+    for n, _ in parts:
+        offs.append(o)
+        o += (n + 127) // 128 * 128
+    assert o <= arena.numel()
+    cnt = len(parts)
+    srcs = (vp * cnt)(*[arena.data_ptr() + 2 * off for off in offs])
+    outs = (vp * cnt)(*[codes.data_ptr() + off for off in offs])
+    ns = (ctypes.c_size_t * cnt)(*[n for n, _ in parts])
+    flags = (ctypes.c_int32 * cnt)(*[f for _, f in parts])
+    sa = torch.zeros(cnt * 2, dtype=torch.float32, device=dev)
+    sp = vp(stream.cuda_stream)
+    if comm is None:
+        comm_h, own = multi_gpu.Comm.single(), True
+    else:
+        comm_h, own = comm, False
+
+    def step():
+        check(lib.cfb200_quant_sym_tensors_sharded(comm_h.handle, cnt, srcs, 2, ns, flags, 8, outs, vp(sa.data_ptr()), sp))
+
+    for _ in range(3):
+        step()
+    ms, per_rank = timed_steps(step, args.steps, stream, barrier, world, dev)
+    if own:
+        comm_h.close()
+    my_bytes = float(sum(n for n, _ in parts) * 2)
+    tot = float(sum(nbytes))
+    share = torch.tensor([my_bytes / tot], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(share, op=dist.ReduceOp.MAX)
+    n_all = sum(r * c for _, r, c in tensors)
+    peak, _ = measured_peak_hbm()
+    val = n_all * ALG_BYTES_PER_ELEM / (ms * 1e-3) / 1e9
+    return {"value": val, "unit": UNIT, "scaling": "strong", "ms_per_step": ms,
+            "workload": "ONE llama3-8b-shaped bf16 set (8.03e9 elements) dealt over all ranks; 128256x4096 tensors cut into row blocks",
+            "frac_of_aggregate_hbm_peak": val / (world * peak), "largest_rank_share_of_bytes": float(share.item()),
+            "rank_ms": per_rank, "slowest_rank": int(max(range(world), key=lambda i: per_rank[i])),
+            "collective": "one grouped ncclAllReduce(MAX) of 2 floats per step" if world > 1 else "none"}
+
+
+def nf4_leg(args, lib, dev, rank, world, arena, codes, barrier, stream):
+    """BASELINE config 3: NF4 block 64 + 8-bit double-quantised absmax (blocks of 256) over ONE Llama-2-7B-shaped bf16 set
+    (6.74e9 elements), tensors dealt whole over the ranks (largest first), no communication.  Algorithmic bytes per
+    element: 2 read + 0.5 + 1/64 + 4/16384 written."""
+    import torch
+    from castforge_b200 import multi_gpu
+    from castforge_b200._lib import check
+    vp = ctypes.c_void_p
+    tensors = llama2_7b_tensors()
+    owner = multi_gpu.shard_assign([r * c * 2 for _, r, c in tensors], world, 0)
+    mine = [(r * c) for (_, r, c), ow in zip(tensors, owner) if ow == rank]
+    offs, o = [], 0
+    for n in mine:
+        offs.append(o)
+        o += (n + 16383) // 16384 * 16384
+    assert o <= arena.numel()
+    nb_tot = o // 64
+    a8 = torch.empty(nb_tot, dtype=torch.uint8, device=dev)
+    a2 = torch.empty(nb_tot // 256 + len(mine), dtype=torch.float32, device=dev)
+    ws_bytes = max(lib.cfb200_quant_nf4_workspace_bytes(n, 64) for n in mine) if mine else 0
+    ws = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
+    sp = vp(stream.cuda_stream)
+
+    def step():
+        for n, off in zip(mine, offs):
+            check(lib.cfb200_quant_nf4(vp(arena.data_ptr() + 2 * off), 2, n, 64, 256, vp(codes.data_ptr() + off // 2),
+                                       vp(a8.data_ptr() + off // 64), vp(a2.data_ptr() + 4 * (off // 16384)), vp(ws.data_ptr()), ws.numel(), sp))
+
+    for _ in range(3):
+        step()
+    ms, per_rank = timed_steps(step, args.steps, stream, barrier, world, dev)
+    n_all = sum(r * c for _, r, c in tensors)
+    alg = 2 + 0.5 + 1 / 64 + 4 / 16384
+    peak, _ = measured_peak_hbm()
+    val = n_all * alg / (ms * 1e-3) / 1e9
+    return {"value": val, "unit": UNIT, "scaling": "strong", "ms_per_step": ms, "gpu_launches_per_step": 2 * len(mine),
+            "workload": "ONE llama2-7b-shaped bf16 set (6.74e9 elements), NF4 block 64 + double-quantised absmax, dealt per tensor over the ranks",
+            "bytes_counted": f"{alg:.4f} B per element (algorithmic)", "frac_of_aggregate_hbm_peak": val / (world * peak), "rank_ms": per_rank}
+
+
+def colpar_leg(args, comm, dev, rank, world, barrier, stream):
+    """Column-parallel GEMMs (every rank owns N / world rows of the [N, K] weight and the whole activation matrix):
+    local tensor-core kernel + ncclAllGather of the bf16 blocks, timed as one unit and with the all-gather's share
+    measured by timing the local kernel alone."""
+    import torch
+    from castforge_b200 import device as D, multi_gpu as mg
+    out = {}
+    g = torch.Generator(device=dev).manual_seed(77)
+    bf16_peak, _ = measured_peak_bf16()
+    hbm, _ = measured_peak_hbm()
+
+    def time_fn(fn, iters=20):
+        for _ in range(3):
+            fn()
+        ms, _ = timed_steps(fn, iters, stream, barrier, world, dev)
+        return ms
+
+    for (M, N, K) in ((2048, 4096, 4096), (8192, 14336, 4096), (8, 128256, 4096)):
+        nl = N // world // 8 * 8
+        a = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        w = (torch.randn(nl, K, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        c4, s4, z4 = D.quant_int4_asym(w.reshape(-1), 128)
+        t_all = time_fn(lambda: mg.gemm_w4a16_colpar(comm, a, c4, s4, z4, nl, 128, layout=0, check_flag=False))
+        if M <= 16:
+            t_loc = time_fn(lambda: D.gemv_w4a16(a, c4, s4, z4, nl, 128))
+            nbytes = world * (nl * K / 2 + 2.5 * nl * K / 128) + 2 * M * K + 2 * M * nl * world
+            out[f"w4a16_decode_M{M}_N{nl * world}_K{K}"] = {"ms": t_all, "local_kernel_ms": t_loc, "allgather_and_interleave_ms": t_all - t_loc,
+                                                            "aggregate_GBps": nbytes / t_all / 1e6, "frac_of_aggregate_hbm_peak": nbytes / t_all / 1e6 / (world * hbm)}
+        else:
+            t_loc = time_fn(lambda: D.gemm_w4a16(a, c4, s4, z4, nl, 128, check=False))
+            tf = 2.0 * M * nl * world * K / t_all / 1e9
+            out[f"w4a16_prefill_{M}x{nl * world}x{K}"] = {"ms": t_all, "local_kernel_ms": t_loc, "allgather_and_interleave_ms": t_all - t_loc,
+                                                          "aggregate_TFLOPps": tf, "frac_of_aggregate_bf16_peak": tf / (world * bf16_peak)}
+            ac, asc = D.cast_e4m3_rows(a)
+            wc, wsa = D.cast_e4m3_tensor(w)
+            wsc = float(wsa[0].item())
+            wc = wc.reshape(nl, K)
+            t_all = time_fn(lambda: mg.gemm_fp8_colpar(comm, ac, asc, wc, wsc, layout=0, check_flag=False))
+            t_loc = time_fn(lambda: D.gemm_fp8(ac, asc, wc, wsc, out_f32=False, check=False))
+            tf = 2.0 * M * nl * world * K / t_all / 1e9
+            out[f"fp8_gemm_{M}x{nl * world}x{K}"] = {"ms": t_all, "local_kernel_ms": t_loc, "allgather_and_interleave_ms": t_all - t_loc,
+                                                     "aggregate_TFLOPps": tf, "frac_of_aggregate_2x_bf16_peak": tf / (world * 2 * bf16_peak)}
+        del a, w
+    out["note"] = ("weights resident and reused between launches (one shape per figure): these are schedule + collective figures, not cold-weight "
+                   "figures; the all-gather is plain NCCL on the kernel's stream")
+    return out
 
 
 def measured_peak_bf16():
@@ -354,7 +587,7 @@ def secondary_metrics(dev):
     back-to-back launches that rotate through distinct weights, so no launch finds its weights in L2):
     W4A16 decode as a fraction of the measured HBM peak, FP8 and W4A16 prefill GEMMs in TFLOP/s."""
     import torch
-    from castforge_b200 import run_case
+    import bench_cases as run_case
     hbm, hbm_src = measured_peak_hbm()
     bf16, bf16_src = measured_peak_bf16()
     out = {}
@@ -385,40 +618,109 @@ def secondary_metrics(dev):
         torch.cuda.empty_cache()
         return ms, flops, nbytes
 
-    for (M, N, K) in ((1, 128256, 4096), (8, 128256, 4096), (8, 14336, 4096)):
+    # BASELINE config 2 (N = K = 4096, M in {1, 8, 16, 128, 2048}) plus the vocabulary- and MLP-sized decode shapes
+    for (M, N, K) in ((1, 4096, 4096), (8, 4096, 4096), (16, 4096, 4096), (1, 128256, 4096), (8, 128256, 4096), (16, 128256, 4096),
+                      (8, 14336, 4096)):
         rot = max(2, min(12, int(400e6 // (N * K / 2)) + 1))   # > 126 MB of distinct weights between reuses
+        if N * K // 2 < (32 << 20):
+            rot = 32                                           # small weights: 32 distinct sets (> 126 MB together)
         ms, _, nbytes = timed("gemv_w4", M, N, K, rot, rot)
         gbs = nbytes / ms / 1e6
         out[f"w4a16_decode_M{M}_N{N}_K{K}"] = {"ms": ms, "GBps": gbs, "frac_of_hbm_peak": gbs / hbm}
-    for (M, N, K) in ((4096, 4096, 4096), (8192, 14336, 4096)):
+    for (M, N, K) in ((4096, 4096, 4096), (8192, 14336, 4096)):   # BASELINE config 4
         ms, flops, _ = timed("gemm_fp8", M, N, K, 3, 6)
         tf = flops / ms / 1e9
         out[f"fp8_gemm_{M}x{N}x{K}"] = {"ms": ms, "TFLOPps": tf, "frac_of_2x_bf16_peak": tf / (2 * bf16)}
-    ms, flops, _ = timed("gemm_w4", 2048, 4096, 4096, 3, 6)
-    tf = flops / ms / 1e9
-    out["w4a16_prefill_2048x4096x4096"] = {"ms": ms, "TFLOPps": tf, "frac_of_bf16_peak": tf / bf16}
+    for (M, N, K) in ((128, 4096, 4096), (2048, 4096, 4096), (8192, 14336, 4096)):
+        ms, flops, _ = timed("gemm_w4", M, N, K, 3, 6)
+        tf = flops / ms / 1e9
+        out[f"w4a16_prefill_{M}x{N}x{K}"] = {"ms": ms, "TFLOPps": tf, "frac_of_bf16_peak": tf / bf16}
+    out["gptq_config5"] = gptq_config5(dev)
     out["peaks"] = {"hbm_GBps": hbm, "hbm_source": hbm_src, "bf16_TFLOPps": bf16, "bf16_source": bf16_src,
                     "fp8_note": "no measured FP8 peak exists; fractions are against 2 x the measured bf16 burst figure"}
     return out
+
+
+def gptq_config5(dev):
+    """BASELINE config 5 on one GPU: 128 x 2048 calibration tokens, bf16 N(0, 1) with a per-channel scale drawn
+    log-uniformly from [0.1, 10]; Hessian (tensor cores, upper triangle), factor, column walk, each timed alone."""
+    import torch
+    from castforge_b200 import device as D
+    out = {}
+    T = 128 * 2048
+    for name, N, K in (("gate_up_14336x4096", 14336, 4096), ("down_4096x14336", 4096, 14336)):
+        g = torch.Generator(device=dev).manual_seed(K)
+        ch = torch.exp((torch.rand(K, device=dev, generator=g) * 2 - 1) * 2.302585)
+        x = torch.empty(T, K, dtype=torch.bfloat16, device=dev)
+        for t0 in range(0, T, 16384):
+            x[t0:t0 + 16384] = (torch.randn(16384, K, device=dev, generator=g) * ch).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=dev, generator=g) * 0.02).to(torch.bfloat16)
+
+        def t3(fn):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            r = fn()
+            e1.record()
+            e1.synchronize()
+            return r, e0.elapsed_time(e1)
+
+        D.gptq_quantize(w[:128].contiguous(), D.gptq_prepare(D.gptq_hessian(x[:1024].contiguous()), 0.01), want_dequant=False)  # warm up
+        h, ms_h = t3(lambda: D.gptq_hessian(x))
+        del x
+        torch.cuda.empty_cache()
+        u, ms_p = t3(lambda: D.gptq_prepare(h, 0.01))
+        _, ms_q = t3(lambda: D.gptq_quantize(w, u, want_dequant=False))
+        out[name] = {"tokens": T, "hessian_ms": ms_h, "hessian_TFLOPps_upper_triangle": T * K * K / ms_h / 1e9, "factor_ms": ms_p,
+                     "quantize_ms": ms_q, "quantize_update_TFLOPps": N * K * K / ms_q / 1e9}
+        del h, u, w
+        torch.cuda.empty_cache()
+    return out
+
+
+def host_memory_available() -> float:
+    """Bytes of host memory this process may still take: MemAvailable, capped by the cgroup limit where there is one."""
+    avail = float("inf")
+    try:
+        for l in open("/proc/meminfo"):
+            if l.startswith("MemAvailable:"):
+                avail = float(l.split()[1]) * 1024
+    except OSError:
+        pass
+    for lim, use in (("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory.current"),
+                     ("/sys/fs/cgroup/memory/memory.limit_in_bytes", "/sys/fs/cgroup/memory/memory.usage_in_bytes")):
+        try:
+            l = open(lim).read().strip()
+            if l != "max":
+                avail = min(avail, float(l) - float(open(use).read().strip()))
+        except (OSError, ValueError):
+            pass
+    return avail
 
 
 def run_e2e(args, lib, dev, rank, world, mine):
     """Same metric through the reference-facing boundary with HOST buffers: a TensorStore of pinned
     bf16 host tensors goes through cfb200_store_run_pipeline("quantize(bits=8)") -- host -> device
     copies, both kernel passes and the copy of codes and scales back to host memory are all inside
-    the timed region.  A bounded subset of the set is streamed per step (PCIe-bound, so the rate
-    does not depend on how many layers are streamed)."""
+    the timed region.  At one GPU the whole set is streamed (16 GB in, 8 GB out per step) when the host has the memory
+    for it; with several ranks, or on a small host, four decoder layers per rank (the rate is PCIe-bound and does not
+    depend on how many layers are streamed).  `copy_only` is the ceiling the figure is read against: the same host
+    buffers copied to the device and the same number of result bytes copied back, on two streams, with no kernel."""
     import torch
     import torch.distributed as dist
     from castforge_b200 import TensorStore
+    layers_req = args.e2e_layers
+    if layers_req < 0:
+        full_bytes = 3.2 * sum(r * c for _, r, c in mine) * 2   # inputs + results + staging, with margin
+        layers_req = 32 if (world == 1 and host_memory_available() > full_bytes) else 4
     layers = [t for t in mine if ".layers." in t[0]]
-    keep = {n for n, _, _ in layers[: 7 * args.e2e_layers]} if args.e2e_layers < 32 else None
+    keep = {n for n, _, _ in layers[: 7 * layers_req]} if layers_req < 32 else None
     sub = sorted([t for t in mine if keep is None or t[0] in keep], key=lambda t: t[0])
     n_sub = sum(r * c for _, r, c in sub)
     h_in = [torch.empty(r * c, dtype=torch.bfloat16).pin_memory() for _, r, c in sub]
     gcpu = torch.Generator().manual_seed(7 + rank)
+    blk = (torch.randn(1 << 22, generator=gcpu) * 0.02).to(torch.bfloat16)
     for h in h_in:
-        blk = (torch.randn(min(h.numel(), 1 << 22), generator=gcpu) * 0.02).to(torch.bfloat16)
         h.copy_(blk.repeat((h.numel() + blk.numel() - 1) // blk.numel())[: h.numel()])
 
     def one_pass():
@@ -434,26 +736,64 @@ def run_e2e(args, lib, dev, rank, world, mine):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(2):
-        one_pass()
-    sync()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        one_pass()
-    torch.cuda.synchronize()
-    dt = (time.perf_counter() - t0) / args.steps
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        sync()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            fn()
+        torch.cuda.synchronize()
+        dt = (time.perf_counter() - t0) / args.steps
+        if world > 1:
+            tt = torch.tensor([dt], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dt = float(tt.item())
+        return dt
+
+    dt = timed(one_pass)
+
+    # copy-only ceiling: same inputs host -> device, as many result bytes device -> host, two streams, three device slots
+    max_n = max(r * c for _, r, c in sub)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    d_in = [torch.empty(max_n, dtype=torch.bfloat16, device=dev) for _ in range(3)]
+    d_out = [torch.zeros(max_n, dtype=torch.int8, device=dev) for _ in range(3)]
+    h_out = [torch.empty(max_n, dtype=torch.int8).pin_memory() for _ in range(3)]
+
+    def copy_pass():
+        done = [None, None, None]
+        for t, h in enumerate(h_in):
+            sl, n = t % 3, h.numel()
+            with torch.cuda.stream(s_in):
+                if done[sl] is not None:
+                    s_in.wait_event(done[sl])
+                d_in[sl][:n].copy_(h, non_blocking=True)
+                e = torch.cuda.Event()
+                e.record(s_in)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(e)
+                h_out[sl][:n].copy_(d_out[sl][:n], non_blocking=True)
+                done[sl] = torch.cuda.Event()
+                done[sl].record(s_out)
+        s_in.synchronize()
+        s_out.synchronize()
+
+    dt_copy = timed(copy_pass)
+    del d_in, d_out, h_out
+
+    n_all = float(n_sub)
     if world > 1:
-        tt = torch.tensor([dt, float(n_sub)], device=dev, dtype=torch.float64)
-        mxv = tt.clone()
-        dist.all_reduce(mxv, op=dist.ReduceOp.MAX)
+        tt = torch.tensor([n_all], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.SUM)
-        dt, n_all = float(mxv[0].item()), float(tt[1].item())
-    else:
-        n_all = n_sub
-    return {"value": n_all * ALG_BYTES_PER_ELEM / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": int(2 * n_sub),
+        n_all = float(tt.item())
+    val = n_all * ALG_BYTES_PER_ELEM / dt / 1e9
+    val_copy = n_all * ALG_BYTES_PER_ELEM / dt_copy / 1e9
+    return {"value": val, "unit": UNIT, "h2d_bytes_per_step": int(2 * n_sub),
             "d2h_bytes_per_step": int(n_sub + 16 * len(sub)),
             "api": "cfb200_store_run_pipeline(store, \"quantize(bits=8)\") on pinned host tensors",
-            "sample": f"{len(sub)} tensors ({n_sub} elements) per GPU streamed from pinned host memory per step", "ms_per_step": dt * 1e3}
+            "sample": f"{len(sub)} tensors ({n_sub} elements) per GPU streamed from pinned host memory per step", "ms_per_step": dt * 1e3,
+            "copy_only_GBps": val_copy, "copy_only_ms_per_step": dt_copy * 1e3, "frac_of_copy_only": val / val_copy,
+            "copy_only_note": "same host buffers copied in and as many result bytes copied out, two streams, no kernels: the host-link ceiling of this figure"}
 
 
 if __name__ == "__main__":

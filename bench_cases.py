@@ -1,8 +1,8 @@
 """Run one entry point of the library on one shape, a few times, and print its device time.
 
-    python -m castforge_b200.run_case e3 --shape 14336x4096 --dtype bf16 --iters 3
-    python -m castforge_b200.run_case gemv_w4 --shape 4x4096x4096
-    python -m castforge_b200.run_case gemm_fp8 --shape 4096x4096x4096
+    python bench_cases.py e3 --shape 14336x4096 --dtype bf16 --iters 3
+    python bench_cases.py gemv_w4 --shape 4x4096x4096
+    python bench_cases.py gemm_fp8 --shape 4096x4096x4096
 
 Meant for timing a kernel in isolation and as the small, self-ending command a profiler wraps.
 Inputs are seeded synthetic data; `--rotate R` cycles through R distinct input buffers so that a
@@ -14,9 +14,12 @@ import argparse
 import json
 import sys
 
+from pathlib import Path
+
 import torch
 
-from . import device as D
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+from castforge_b200 import device as D  # noqa: E402
 
 HBM_CASES = ("a1", "a1list", "a1layer", "gguf_q8_pack", "gguf_q8_unpack", "gguf_q4_unpack", "e1", "e2", "e3", "e4rows", "e4tensor", "a2", "a2awq", "a3", "a4", "a6", "fwht",
              "kv_page", "kv_head", "kv_tensor", "kv_decode", "e4m3_slice_enc", "e4m3_slice_dec",
@@ -163,7 +166,7 @@ def stream_file_case(layers, iters):
 
     import numpy as np
 
-    from . import TensorStore
+    from castforge_b200 import TensorStore
     root = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else None
     out = {"case": "stream_file", "layers": layers, "tmp_root": root or tempfile.gettempdir()}
     with tempfile.TemporaryDirectory(dir=root) as tmp:
@@ -217,12 +220,12 @@ def main(argv=None):
     ap.add_argument("--tune", action="append", default=[], metavar="KEY=VALUE", help="performance knob for cfb200_tune")
     args = ap.parse_args(argv)
     for kv in args.tune:
-        from . import load
+        from castforge_b200 import load
         key, _, val = kv.partition("=")
         if load().cfb200_tune(key.encode(), int(val)) != 0:
             raise SystemExit(f"unknown tunable {key!r}")
     if not torch.cuda.is_available():
-        raise SystemExit("run_case needs a CUDA device")
+        raise SystemExit("bench_cases.py needs a CUDA device")
     dev = torch.device("cuda:0")
     dt = {"bf16": torch.bfloat16, "f16": torch.float16, "f32": torch.float32}[args.dtype]
     if args.case == "stream_file":  # --shape LAYERSx1: a .safetensors file of LAYERS Llama-3-8B decoder layers (bf16)

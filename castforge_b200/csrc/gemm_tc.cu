@@ -49,6 +49,7 @@ struct GemmArgs {
   int ldc;
   int out_f32;
   int upper_only;           // skip tiles strictly below the diagonal (symmetric products)
+  int accumulate;           // f32 output only: C += result instead of C = result
   int* error_flag;          // device int, set non-zero when a bounded wait ran out
   int split_k;              // > 1: a tile's k-blocks are dealt to split_k CTAs, raw f32 partial sums go to `partial`
   float* partial;           // [split_k][M][N] f32 (split_k > 1 only)
@@ -440,9 +441,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               if (col0 + j < args.N) dst[j] = __uint_as_float(r[j]);
           } else if (args.out_f32) {
             float* dst = reinterpret_cast<float*>(args.C) + (size_t)row * args.ldc + col0;
+            if (args.accumulate) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) dst[j] = __uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f);
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < args.N) dst[j] = __fadd_rn(dst[j], __uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < args.N) dst[j] = __uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f);
+            }
           } else {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(args.C) + (size_t)row * args.ldc + col0;
             if (col0 + 32 <= args.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
@@ -568,20 +575,31 @@ extern "C" int32_t cfb200_gemm_fp8(const uint8_t* A, const float* a_scales, cons
   return launch_gemm<256, kKindE4M3, kBTma, 4>(tmA, tmB, g, (cudaStream_t)stream);
 }
 
-extern "C" int32_t cfb200_gemm_bf16_nt(const void* A, const void* B, size_t M, size_t N, size_t K, float alpha, void* C,
-                                       int32_t out_f32, int32_t upper_only, int32_t* error_flag, void* stream) {
+// The bf16 product with explicit row pitches (lda, ldb in elements: the operands may be column ranges of wider
+// matrices) and an optional C += (f32 output only).
+extern "C" int32_t cfb200_gemm_bf16_nt_ld(const void* A, size_t lda, const void* B, size_t ldb, size_t M, size_t N, size_t K,
+                                          float alpha, void* C, int32_t out_f32, int32_t upper_only, int32_t accumulate,
+                                          int32_t* error_flag, void* stream) {
   CFB_CHECK_ARG(A && B && C, "NULL buffer");
   CFB_CHECK_ARG(M > 0 && N > 0 && K > 0 && K % 8 == 0, "bf16 GEMM needs K a positive multiple of 8 (got %zu)", K);
   CFB_CHECK_ARG(M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "dimension too large");
+  CFB_CHECK_ARG(lda >= K && ldb >= K, "row pitch shorter than K");
+  CFB_CHECK_ARG(!accumulate || out_f32, "accumulation needs an f32 output");
   CUtensorMap tmA, tmB;
-  int32_t rc = make_tmap(&tmA, A, 2, M, K, K, kBM);
+  int32_t rc = make_tmap(&tmA, A, 2, M, K, lda, kBM);
   if (rc) return rc;
-  rc = make_tmap(&tmB, B, 2, N, K, K, 128);
+  rc = make_tmap(&tmB, B, 2, N, K, ldb, 128);
   if (rc) return rc;
   GemmArgs g = {};
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
-  g.alpha = alpha; g.C = C; g.ldc = (int)N; g.out_f32 = out_f32; g.upper_only = upper_only; g.error_flag = error_flag;
+  g.alpha = alpha; g.C = C; g.ldc = (int)N; g.out_f32 = out_f32; g.upper_only = upper_only; g.accumulate = accumulate;
+  g.error_flag = error_flag;
   return launch_gemm<128, kKindBF16, kBTma, 6>(tmA, tmB, g, (cudaStream_t)stream);
+}
+
+extern "C" int32_t cfb200_gemm_bf16_nt(const void* A, const void* B, size_t M, size_t N, size_t K, float alpha, void* C,
+                                       int32_t out_f32, int32_t upper_only, int32_t* error_flag, void* stream) {
+  return cfb200_gemm_bf16_nt_ld(A, K, B, K, M, N, K, alpha, C, out_f32, upper_only, 0, error_flag, stream);
 }
 
 namespace cfb {

@@ -116,7 +116,7 @@ def _aligned(ws: torch.Tensor):
 
 
 def gemm_w4a16_colpar(comm: Comm, a: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, zps: torch.Tensor, n_local: int,
-                      group: int = 128, layout: int = 0) -> torch.Tensor:
+                      group: int = 128, layout: int = 0, check_flag: bool = True) -> torch.Tensor:
     """Column-parallel W4A16 product: this rank's [n_local, K] weight shard in, the whole bf16 product out
     ([M, world * n_local] for layout 0, [world, M, n_local] for layout 1)."""
     a = a.contiguous()
@@ -129,12 +129,13 @@ def gemm_w4a16_colpar(comm: Comm, a: torch.Tensor, codes: torch.Tensor, scales: 
         flag = torch.zeros(1, dtype=torch.int32, device=dev)
         check(load().cfb200_gemm_w4a16_colpar(comm.handle, _p(a), _p(codes), _p(scales), _p(zps), M, n_local, K, group, _p(c), layout,
                                               _aligned(ws), need, _p(flag), _stream(dev)))
-        if int(flag.item()) != 0:
+        if check_flag and int(flag.item()) != 0:  # reading the flag synchronises: timing loops pass check_flag=False
             raise RuntimeError("gemm_w4a16_colpar: a bounded wait ran out inside the kernel")
     return c
 
 
-def gemm_fp8_colpar(comm: Comm, a_codes: torch.Tensor, a_scales, w_codes_local: torch.Tensor, w_scale: float, layout: int = 0) -> torch.Tensor:
+def gemm_fp8_colpar(comm: Comm, a_codes: torch.Tensor, a_scales, w_codes_local: torch.Tensor, w_scale: float, layout: int = 0,
+                    check_flag: bool = True) -> torch.Tensor:
     """Column-parallel FP8 product (per-token x per-tensor scales): [n_local, K] weight shard in, whole bf16 product out."""
     a_codes = a_codes.contiguous()
     M, K = a_codes.shape
@@ -147,7 +148,7 @@ def gemm_fp8_colpar(comm: Comm, a_codes: torch.Tensor, a_scales, w_codes_local: 
         flag = torch.zeros(1, dtype=torch.int32, device=dev)
         check(load().cfb200_gemm_fp8_colpar(comm.handle, _p(a_codes), _p(a_scales), _p(w_codes_local), float(w_scale), M, n_local, K,
                                             _p(c), layout, _aligned(ws), need, _p(flag), _stream(dev)))
-        if int(flag.item()) != 0:
+        if check_flag and int(flag.item()) != 0:
             raise RuntimeError("gemm_fp8_colpar: a bounded wait ran out inside the kernel")
     return c
 

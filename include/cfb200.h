@@ -257,6 +257,11 @@ int32_t cfb200_gemm_fp8(const uint8_t* A, const float* a_scales, const uint8_t* 
 int32_t cfb200_gemm_bf16_nt(const void* A, const void* B, size_t M, size_t N, size_t K, float alpha,
                             void* C, int32_t out_f32, int32_t upper_only, int32_t* error_flag,
                             void* stream);
+/* cfb200_gemm_bf16_nt with explicit row pitches (lda, ldb in elements, multiples of 8: the operands may be column
+ * ranges of wider matrices) and `accumulate` (f32 output only): C += alpha * acc, one rounded f32 addition per element. */
+int32_t cfb200_gemm_bf16_nt_ld(const void* A, size_t lda, const void* B, size_t ldb, size_t M, size_t N, size_t K,
+                               float alpha, void* C, int32_t out_f32, int32_t upper_only, int32_t accumulate,
+                               int32_t* error_flag, void* stream);
 size_t cfb200_gemm_w4a16_workspace_bytes(size_t M, size_t N, size_t K);
 int32_t cfb200_gemm_w4a16(const void* A, const uint8_t* w_codes, const uint16_t* w_scales,
                           const uint8_t* w_zps, size_t M, size_t N, size_t K, size_t group, void* C,

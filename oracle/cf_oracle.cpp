@@ -866,6 +866,75 @@ int cfo_gptq(const float* W, const float* X, size_t N, size_t K, size_t T, size_
   return 0;
 }
 
+// The GPTQ column walk in the device kernels' own arithmetic: f32 state, every operation in the order
+// castforge_b200/csrc/gptq.cu performs it, so that codes, scales and zero points can be compared with `==` (cfo_gptq
+// above keeps f64 state and differs from any f32 walk on near-ties).  No reference counterpart (GPTQ is absent from
+// the reference, src/passes/quantize/schemes.rs:115-121); this restates the product's specification:
+//   per block of 128 columns (= one group): lo / hi over the row's CURRENT values, scale = truncating f16 of
+//   (hi - lo) / 15 (0 / inf / NaN -> 1.0), zp = clamp(round(-lo / s), 0, 15);
+//   per column j of the block: q = clamp(round(w / s) + zp), wq = (q - zp) * s, e = (w - wq) / U[j][j],
+//     then w[c] = fma(-e, U[j][c], w[c]) for the block's later columns c (j ascending);
+//   after the block: for every later column n, acc = 0; acc = fma(e[k], U[b + k][n], acc) for k = 0..127; w[n] -= acc.
+// W: `rows` rows of K f32 values (already widened); U: K x K f32, row-major (the factor the device computed).
+// zps_unpacked: one byte per group.  Wdq: NULL or rows x K.
+void cfo_gptq_walk_f32(const float* W, size_t rows, size_t K, const float* U, uint8_t* codes, uint16_t* scales,
+                       uint8_t* zps_unpacked, float* Wdq, int threads) {
+  const size_t groups = K / 128;
+  int t = set_threads(threads);
+  std::vector<float> state(W, W + rows * K);  // every row's current values
+  // block-major: all rows walk block b before any row walks block b + 1 (rows are independent, so the order across
+  // rows changes nothing); the 128 rows of U a block needs then stay in cache for every row
+  for (size_t b = 0; b < K; b += 128) {
+    const size_t rest = K - b - 128;
+#ifdef _OPENMP
+#pragma omp parallel for num_threads(t) schedule(static) if (t > 1)
+#endif
+    for (long long r = 0; r < (long long)rows; ++r) {
+      float* w = state.data() + (size_t)r * K;
+      float e[128];
+      float lo = 0.0f, hi = 0.0f;
+      for (size_t i = b; i < b + 128; ++i) { lo = std::fmin(lo, w[i]); hi = std::fmax(hi, w[i]); }
+      uint16_t sh = cfo_f32_to_f16_bits((hi - lo) / 15.0f);
+      if ((sh & 0x7fffu) == 0 || (sh & 0x7c00u) == 0x7c00u) sh = 0x3c00u;
+      const float sc = cfo_f16_bits_to_f32(sh);
+      float zf = std::round(-lo / sc);
+      zf = (zf != zf) ? 0.0f : std::fmin(std::fmax(zf, 0.0f), 15.0f);
+      scales[(size_t)r * groups + b / 128] = sh;
+      zps_unpacked[(size_t)r * groups + b / 128] = (uint8_t)zf;
+      for (size_t j = 0; j < 128; ++j) {
+        const float wj = w[b + j];
+        float qf = std::round(wj / sc) + zf;
+        qf = (qf != qf) ? 0.0f : std::fmin(std::fmax(qf, 0.0f), 15.0f);
+        const float wq = (qf - zf) * sc;
+        const float ej = (wj - wq) / U[(b + j) * K + b + j];
+        e[j] = ej;
+        w[b + j] = wq;
+        const size_t idx = (size_t)r * K + b + j;
+        const uint8_t c = (uint8_t)qf;
+        if ((idx & 1) == 0) codes[idx >> 1] = (uint8_t)((codes[idx >> 1] & 0xF0) | c);
+        else codes[idx >> 1] = (uint8_t)((codes[idx >> 1] & 0x0F) | (c << 4));
+        const float* urow = U + (b + j) * K + b;
+        for (size_t c2 = j + 1; c2 < 128; ++c2) w[b + c2] = std::fma(-ej, urow[c2], w[b + c2]);
+      }
+      // the block's errors into every later column: k outermost so that U is read along its rows; each column's sum
+      // still adds k = 0..127 in ascending order into its own accumulator, which starts at zero
+      if (rest) {
+        std::vector<float> acc(rest, 0.0f);
+        float* ap = acc.data();
+        for (size_t k = 0; k < 128; ++k) {
+          const float ek = e[k];
+          const float* urow = U + (b + k) * K + b + 128;
+#pragma omp simd
+          for (size_t n = 0; n < rest; ++n) ap[n] = std::fma(ek, urow[n], ap[n]);
+        }
+        float* wr = w + b + 128;
+        for (size_t n = 0; n < rest; ++n) wr[n] = wr[n] - ap[n];
+      }
+    }
+  }
+  if (Wdq) std::memcpy(Wdq, state.data(), rows * K * sizeof(float));
+}
+
 // GGUF Q8_0 export of a per-tensor INT8 tensor (gguf.rs:283-296) and the Q8_0 / Q4_0 decoders (:513-552).
 size_t cfo_gguf_pack_q8_0(const int8_t* codes, size_t n, float scale, uint8_t* out) {
   size_t blocks = ((n > 0 ? n : 1) + 31) / 32;

@@ -113,11 +113,13 @@ def check_gptq(comm, dev, rank, world):
     ng = K // 128
     assert torch.equal(c_l, codes[lo * K // 2: hi * K // 2]), "GPTQ codes of the row shard differ"
     assert torch.equal(s_l.view(torch.int16), scales.view(torch.int16)[lo * ng: hi * ng]) and torch.equal(z_l, zps[lo * ng // 2: hi * ng // 2])
-    # token-parallel Hessian: the sum over ranks adds in another order, so equality is to rounding
+    # token-parallel Hessian: the sum over ranks adds in another order, so equality is to rounding.  The error is
+    # measured against the RMS of H while the largest entries (diagonal, channel scale up to 10) are ~100 x the RMS,
+    # and the tensor cores' f32 accumulation is good to ~1e-5 of the VALUE: bound 1e-3 of the RMS.
     tl0, tl1 = mg.shard_row_range(T, world, rank, 8)
     h2 = mg.gptq_hessian_sharded(comm, x[tl0:tl1].contiguous(), T)
     torch.cuda.synchronize()
-    assert rel_err(h2, h) < 1e-5, rel_err(h2, h)
+    assert rel_err(h2, h) < 1e-3, rel_err(h2, h)
     return True
 
 

@@ -271,6 +271,23 @@ class Oracle:
             raise ValueError("Hessian not positive definite")
         return codes, scales, zps, wdq
 
+    def gptq_walk_f32(self, W, U, want_dequant=False, threads=0):
+        """E5 column walk in the device kernels' f32 operation order.  W [rows, K] f32 values, U [K, K] f32 (the factor
+        the device computed).  Returns codes [rows * K / 2], scales u16 [rows * K / 128], zero points (one byte per
+        group) and, on request, the dequantised rows."""
+        W = np.ascontiguousarray(W, np.float32)
+        U = np.ascontiguousarray(U, np.float32)
+        rows, K = W.shape
+        assert U.shape == (K, K) and K % 128 == 0
+        codes = np.zeros(rows * K // 2, np.uint8)
+        scales = np.zeros(rows * (K // 128), np.uint16)
+        zps = np.zeros(rows * (K // 128), np.uint8)
+        wdq = np.empty((rows, K), np.float32) if want_dequant else None
+        self.lib.cfo_gptq_walk_f32.restype = None
+        self.lib.cfo_gptq_walk_f32(_ptr(W), c_sz(rows), c_sz(K), _ptr(U), _ptr(codes), _ptr(scales), _ptr(zps),
+                                   _ptr(wdq) if want_dequant else None, c_i(threads))
+        return codes, scales, zps, wdq
+
     def gguf_pack_q8_0(self, codes, scale):
         codes = np.ascontiguousarray(codes, np.int8).reshape(-1)
         out = np.zeros(((max(codes.size, 1) + 31) // 32) * 34, np.uint8)

@@ -1,11 +1,14 @@
 """E5 (GPTQ INT4, group 128): the f64 oracle against an independent numpy statement of the algorithm
 (CPU), and the CUDA path against the oracle (GPU).
 
-The CUDA path keeps its state in f32 and the oracle in f64, so a code can differ where a value lands
-within rounding error of a quantisation boundary; a differing code then changes the errors pushed to
-the right of it.  The tests therefore bound the fraction of differing codes and compare the quantity
-GPTQ minimises, the layer output error ||X (W - W_hat)||, which must agree closely and must beat
-plain round-to-nearest with the same group format."""
+Two oracles.  `gptq` keeps its state in f64 (the algorithm as published); the CUDA path keeps f32 state, so against it
+a code can differ where a value lands within rounding error of a quantisation boundary, and a differing code changes
+the errors pushed to the right of it: those tests bound the fraction of differing codes and compare the quantity GPTQ
+minimises, the layer output error ||X (W - W_hat)||.  `gptq_walk_f32` restates the column walk in the device's own f32
+operation order, given the factor U the device computed: codes, scales and zero points must then be EQUAL, at the
+small shapes and at BASELINE config 5's sizes (K = 4096 and K = 14336, T = 262144 calibration tokens) on sampled
+rows.  The factor itself is checked against f64 (np.linalg at small K; at config size through U^T U (H + damp) v = v on
+random vectors, which needs no second factorisation)."""
 import numpy as np
 import pytest
 
@@ -88,6 +91,114 @@ def test_oracle_beats_round_to_nearest(oracle):
     c, s, z = oracle.quant_int4_asym(W.reshape(-1), 128)
     rtn = oracle.dequant_int4_asym(c, s, z, W.size, 128).reshape(W.shape)
     assert out_err(X, W, wdq) < 0.9 * out_err(X, W, rtn)
+
+
+def test_f32_order_walk_agrees_with_the_f64_oracle(oracle):
+    """The f32-order walk is the same algorithm: given the f64 factor (rounded to f32) it lands within boundary effects
+    of the f64 oracle, and what it returns decodes to its own dequantised rows."""
+    W, X = make_case(21, 48, 256, 1024)
+    T, K = X.shape
+    H = (X.astype(np.float64).T @ X.astype(np.float64)) / T
+    H[np.diag_indices(K)] += 0.01 * np.mean(np.diag(H))
+    U = np.linalg.cholesky(np.linalg.inv(H)).T.astype(np.float32)
+    codes, scales, zpb, wdq = oracle.gptq_walk_f32(W, U, want_dequant=True)
+    oc, osc, oz, owdq = oracle.gptq(W, X)
+    assert (unpack(codes, W.size) != unpack(oc, W.size)).mean() < 0.02
+    assert abs(out_err(X, W, wdq) - out_err(X, W, owdq)) <= 0.02 * out_err(X, W, owdq)
+    zp_packed = (zpb[0::2] | (zpb[1::2] << 4)).astype(np.uint8)
+    np.testing.assert_array_equal(oracle.dequant_int4_asym(codes, scales, zp_packed, W.size, 128).reshape(W.shape), wdq)
+
+
+def _unpack_zps(zps, ngroups):
+    z = np.asarray(zps, np.uint8)
+    out = np.empty(z.size * 2, np.uint8)
+    out[0::2] = z & 0xF
+    out[1::2] = z >> 4
+    return out[:ngroups]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,K,T", [(64, 256, 1024), (200, 512, 2048), (8, 128, 256), (96, 1024, 4096)])
+def test_gptq_cuda_equals_f32_order_oracle(oracle, cuda_device, N, K, T):
+    """Codes, scales, zero points and dequantised weights EQUAL the f32-order oracle's, given the device's factor."""
+    import torch
+    from castforge_b200 import device as D
+    W, X = make_case(N + K + 1, N, K, T)
+    W, X = bf16_round(W), bf16_round(X)
+    xd = torch.from_numpy(X).to(cuda_device, torch.bfloat16)
+    wd = torch.from_numpy(W).to(cuda_device, torch.bfloat16)
+    U = D.gptq_prepare(D.gptq_hessian(xd), 0.01)
+    codes, scales, zps, wdq = D.gptq_quantize(wd, U)
+    torch.cuda.synchronize()
+    oc, osc, ozb, owdq = oracle.gptq_walk_f32(W, U.cpu().numpy(), want_dequant=True)
+    np.testing.assert_array_equal(codes.cpu().numpy(), oc)
+    np.testing.assert_array_equal(scales.cpu().numpy().view(np.uint16), osc)
+    np.testing.assert_array_equal(_unpack_zps(zps.cpu().numpy(), N * (K // 128)), ozb)
+    np.testing.assert_array_equal(wdq.cpu().numpy(), owdq)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("N,K", [(14336, 4096), (4096, 14336)])
+def test_gptq_config5_sizes(oracle, cuda_device, N, K):
+    """BASELINE config 5 at its own sizes: gate / up (14336 x 4096) and down (4096 x 14336), 128 x 2048 = 262144
+    calibration tokens, bf16 N(0, 1) activations with a per-channel scale drawn log-uniformly from [0.1, 10], 1 %
+    damping, group 128.  Hessian entries against f64 sums, the factor through U^T U (H + damp) v = v, and the codes /
+    scales / zero points of 64 sampled output rows EQUAL to the f32-order oracle's (rows are independent)."""
+    import torch
+    from castforge_b200 import device as D
+    T = 128 * 2048
+    g = torch.Generator(device=cuda_device).manual_seed(K)
+    ch = torch.exp((torch.rand(K, device=cuda_device, generator=g) * 2 - 1) * float(np.log(10.0)))
+    X = torch.empty(T, K, dtype=torch.bfloat16, device=cuda_device)
+    for t0 in range(0, T, 16384):
+        X[t0:t0 + 16384] = (torch.randn(16384, K, device=cuda_device, generator=g) * ch).to(torch.bfloat16)
+    W = (torch.randn(N, K, device=cuda_device, generator=g) * 0.02).to(torch.bfloat16)
+    H = D.gptq_hessian(X)
+    # Hessian: 48 sampled entries (diagonal and off-diagonal) against f64 sums of the same bf16 values
+    rng = np.random.default_rng(K)
+    ii = rng.integers(0, K, 48)
+    jj = np.where(np.arange(48) % 2 == 0, ii, rng.integers(0, K, 48))
+    cols = torch.from_numpy(np.unique(np.concatenate([ii, jj]))).to(cuda_device)
+    Xs = X[:, cols].double().cpu().numpy()
+    pos = {int(c): k for k, c in enumerate(cols.cpu().numpy())}
+    Hh = H.cpu().numpy()
+    for i, j in zip(ii, jj):
+        want = float(Xs[:, pos[int(i)]] @ Xs[:, pos[int(j)]]) / T
+        # 32 chunk sums of 512 truncating tensor-core additions each, then round-to-nearest additions: measured 3e-5
+        assert abs(float(Hh[i, j]) - want) <= 1e-4 * np.sqrt(Hh[i, i] * Hh[j, j]) + 1e-7, (i, j, Hh[i, j], want)
+    del X, Xs
+    torch.cuda.empty_cache()
+    U = D.gptq_prepare(H, 0.01)
+    Uh = U.cpu().numpy()
+    assert np.all(np.diag(Uh) > 0) and float(np.abs(np.tril(Uh, -1)).max()) == 0.0
+    # factor: (U^T U) (H + damp I) v = v in f64 for random v (U^T U = inverse of the damped Hessian)
+    Hd = Hh.astype(np.float64)
+    Hd[np.diag_indices(K)] += 0.01 * float(np.mean(np.diag(Hh).astype(np.float64)))
+    V = rng.standard_normal((K, 4))
+    Y = Uh.T.astype(np.float64) @ (Uh.astype(np.float64) @ (Hd @ V))
+    resid = float(np.linalg.norm(Y - V) / np.linalg.norm(V))
+    assert resid < 5e-3, resid   # f32 factorisation of a matrix with condition number ~1e3
+    del Hd
+    codes, scales, zps, wdq = D.gptq_quantize(W, U, want_dequant=True)
+    torch.cuda.synchronize()
+    rows = np.sort(rng.choice(N, 64, replace=False))
+    Wr = W[torch.from_numpy(rows).to(cuda_device)].float().cpu().numpy()
+    oc, osc, ozb, owdq = oracle.gptq_walk_f32(Wr, Uh, want_dequant=True)
+    ng = K // 128
+    ch_, sh_, zh_ = codes.cpu().numpy().reshape(N, K // 2), scales.cpu().numpy().view(np.uint16).reshape(N, ng), _unpack_zps(zps.cpu().numpy(), N * ng).reshape(N, ng)
+    np.testing.assert_array_equal(ch_[rows], oc.reshape(64, K // 2))
+    np.testing.assert_array_equal(sh_[rows], osc.reshape(64, ng))
+    np.testing.assert_array_equal(zh_[rows], ozb.reshape(64, ng))
+    np.testing.assert_array_equal(wdq[torch.from_numpy(rows).to(cuda_device)].cpu().numpy(), owdq)
+    # and the point of it all: a lower layer-output error than round-to-nearest in the same format, on those rows
+    # (||X d||^2 = T d H d^T)
+    c2, s2, z2 = oracle.quant_int4_asym(Wr.reshape(-1), 128)
+    rtn = oracle.dequant_int4_asym(c2, s2, z2, Wr.size, 128).reshape(64, K)
+    H64 = Hh.astype(np.float64)
+    def err(d):
+        d = d.astype(np.float64)
+        return float(np.sqrt(np.einsum("rk,rk->", d @ H64, d)))
+    assert err(Wr - owdq) < 0.9 * err(Wr - rtn)
 
 
 @pytest.mark.gpu

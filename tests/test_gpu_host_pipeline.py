@@ -161,3 +161,55 @@ def test_store_fake_quant_and_extension_schemes(cuda_device, oracle):
     assert np.array_equal(e["w"]["data"], c) and np.array_equal(e["w.absmax8"]["data"], a8) and np.array_equal(e["w.absmax2"]["data"], a2)
     e = run("quantize(scheme=nonsense_name)")                                 # unknown scheme strings mean per-tensor weights (schemes.rs:114-150)
     assert e["w"]["quantized"] and np.array_equal(e["w"]["data"], oracle.quant_sym(w, 8)[0])
+
+
+def test_two_host_threads_share_one_device(cuda_device):
+    """The C ABI is re-entrant like the reference's: two host threads run quantize pipelines on the same device at the
+    same time (the per-device staging slots are handed from one call to the next under a lock) and each gets exactly
+    what a serial run gives."""
+    import threading
+    rng = np.random.default_rng(3)
+    sets = [[(rng.standard_normal((257, 130 + 7 * k + t)) * 0.02).astype(np.float32) for k in range(6)] for t in range(2)]
+
+    def run(ws, spec):
+        st = cfb.TensorStore()
+        for i, w in enumerate(ws):
+            st.insert(f"w{i}", w)
+        st.run_pipeline(spec)
+        out = {n: (e["data"].copy(), e["scale"]) for n, e in st.entries().items()}
+        st.close()
+        return out
+
+    specs = ["quantize(bits=8)", "quantize(scheme=nf4)"]
+    serial = [run(sets[t], specs[t]) for t in range(2)]
+    for _ in range(3):
+        got = [None, None]
+        errs = []
+
+        def work(t):
+            try:
+                got[t] = run(sets[t], specs[t])
+            except Exception as e:  # noqa: BLE001
+                errs.append(e)
+        th = [threading.Thread(target=work, args=(t,)) for t in range(2)]
+        for x in th:
+            x.start()
+        for x in th:
+            x.join()
+        assert not errs, errs
+        for t in range(2):
+            assert got[t].keys() == serial[t].keys()
+            for n in serial[t]:
+                assert np.array_equal(got[t][n][0], serial[t][n][0]) and got[t][n][1] == serial[t][n][1], (t, n)
+
+
+def test_a1_status_word_reads_zero_after_normal_runs(cuda_device):
+    """cfb200_quant_sym_status: the persistent kernel's bounded waits have not run out (nothing here makes one expire)."""
+    import ctypes
+    import torch
+    from castforge_b200 import device as D
+    w = (torch.randn(24 << 20, device=cuda_device) * 0.02).to(torch.bfloat16)   # 48 MB: takes the persistent kernel
+    D.quant_sym_tensor(w, 8)
+    D.quant_sym_tensors([w[: 1 << 20], w[1 << 20: 3 << 20]], 8)
+    flag = ctypes.c_int32(-1)
+    assert cfb.load().cfb200_quant_sym_status(ctypes.byref(flag)) == 0 and flag.value == 0

@@ -133,9 +133,28 @@ def test_safetensors_hardening():
                      (blob({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 16]}}, b"\0" * 8), "Invalid data_offsets"),
                      (blob({"a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]}, "b": {"dtype": "F32", "shape": [1], "data_offsets": [2, 6]}}, b"\0" * 8), "Overlapping"),
                      (blob({"a": {"dtype": "F32", "shape": [3], "data_offsets": [0, 8]}}, b"\0" * 8), "does not match shape"),
-                     (blob({"a": {"dtype": "C64", "shape": [1], "data_offsets": [0, 8]}}, b"\0" * 8), "Unsupported safetensors dtype")]:
+                     (blob({"a": {"dtype": "F32", "shape": [2], "data_offsets": [-8, 0]}}, b"\0" * 8), "non-negative integer"),
+                     (blob({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0.5, 8]}}, b"\0" * 8), "non-negative integer"),
+                     (blob({"a": {"dtype": "F32", "shape": [2], "data_offsets": ["0", 8]}}, b"\0" * 8), "non-negative integer")]:
         with pytest.raises(cfb.CastForgeError, match=msg):
             st.load_safetensors_bytes(bad)
+
+
+def test_safetensors_unknown_dtype_is_kept_as_raw_bytes(tmp_path):
+    """A dtype the store has no arithmetic for (I64 position ids, BOOL masks, F64 ...) loads as an opaque U8 entry holding
+    the raw bytes of its slice, like the reference's reader (src/ir/tensor_store.rs:742-750), and the quantize passes
+    leave it alone; the float tensor beside it is still quantized."""
+    ids = np.arange(5, dtype=np.int64)
+    w = (np.arange(8, dtype=np.float32) - 4) * np.float32(0.25)
+    meta = {"position_ids": {"dtype": "I64", "shape": [5], "data_offsets": [0, 40]},
+            "w": {"dtype": "F32", "shape": [2, 4], "data_offsets": [40, 72]}}
+    h = json.dumps(meta).encode()
+    st = cfb.TensorStore()
+    st.load_safetensors_bytes(struct.pack("<Q", len(h)) + h + ids.tobytes() + w.tobytes())
+    e = st.entries()
+    assert e["position_ids"]["dtype"] == 4 and e["position_ids"]["shape"] == [5]
+    assert e["position_ids"]["data"].tobytes() == ids.tobytes()
+    assert np.array_equal(e["w"]["data"], w)
 
 
 def test_safetensors_lazy_file(tmp_path):
