@@ -28,9 +28,8 @@ enum Tunable {
   kTuneGemvRing = 6,   // decode W4A16: large shapes go through the shared-memory ring kernel
   kTuneGemvRingRounds = 7,  // row blocks per cluster the ring kernel asks for before it splits K further (0 = default 1)
   kTuneW4SplitK = 8,   // W4A16 prefill: 0 = automatic split-K for M <= 256, 1 = never, n > 1 = at most n slices
-  kTuneA1Prefetch = 9, // persistent A1: 32 KB items per CTA requested into L2 across a grid barrier
-  kTuneA1BarSleep = 10, // persistent A1: nanoseconds between two polls of the grid barrier (0 = poll back to back)
-  kTuneA1TailFirst = 11, // persistent A1: the quantize pass re-reads the lines kept in L2 before the ones that were let go
+  kTuneA1BarSleep = 9, // persistent A1: nanoseconds between two polls of the grid barrier (0 = poll back to back)
+  kTuneA1TailFirst = 10, // persistent A1: the quantize pass re-reads the lines kept in L2 before the ones that were let go
   kTuneCount
 };
 long long tunable(int id);

@@ -543,7 +543,7 @@ __device__ __forceinline__ uint32_t items_of(const PGroup& grp, uint32_t bid, ui
 template <int DT>
 __global__ void __launch_bounds__(kPThreads, 1)
 a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float qmin, float qmax, uint32_t retain_items,
-                  uint32_t prefetch_items, uint32_t bar_sleep_ns, uint32_t tail_first) {
+                  uint32_t bar_sleep_ns, uint32_t tail_first) {
   constexpr int VE = Vec16<DT>::kElems;
   constexpr int VPT = kPItemVecs / kPConsumers;  // vectors per consumer thread per item
   static_assert(kPItemVecs % kPConsumers == 0 && VPT % 4 == 0, "the unrolled quantize loop reads four vectors per thread per trip");
@@ -639,6 +639,20 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
     if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty0 + 8 * b) : "memory");
   };
 
+  // A bounded wait ran out: copies already issued still write into this CTA's shared memory, so wait (bounded again)
+  // for each of them before the CTA returns, and report through the sticky device flag.
+  auto fail_exit = [&]() {
+    if (tid == 0) {
+      g_pflag = 1;
+      for (uint32_t j = seq; j < s_issued; ++j) {
+        const int b = (int)(j % kPBufs);
+        if (!mbar_wait_bounded(full0 + 8 * b, (full_par >> b) & 1u)) break;
+        full_par ^= 1u << b;
+      }
+    }
+    __syncthreads();
+  };
+
   // phase p: quantize group p (s_grp[(p + 3) % 3], absent for p == -1) under the absmax pass of group p + 1
   for (int p = -1;; ++p) {
     PGroup& cur = s_grp[(p + 3) % 3];
@@ -674,29 +688,7 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
       }
       __syncwarp();
       // the group after next, for the following phase (its slot held group p - 1, which is done)
-      PGroup& nn = s_grp[(p + 2) % 3];
-      setup_group<VE>(nn, segs, count, nxt.nseg ? nxt.end : count, lane);
-      // Every ring buffer now holds (or is about to receive) an item that stays until the scale of the next group is
-      // known, so no copy into shared memory can be issued before the grid barrier.  L2 needs no buffer: the first
-      // items of the next phase (reloads of the next group, first lines of the group after it) are requested into L2
-      // now, which keeps HBM busy across the barrier; the copies issued after it find them there.
-      if (lane == 0 && prefetch_items != 0 && nxt.nseg != 0) {
-        const uint32_t Tc2 = Tn, Tn2 = items_of(nn, bid, G);
-        const uint32_t A2 = Tc2 > (uint32_t)kPBufs ? Tc2 - kPBufs : 0;
-        const uint32_t B2 = Tn2, Bf2 = Tn2 > (uint32_t)kPBufs ? Tn2 - kPBufs : 0;
-        const uint32_t Rk2 = tail_first ? (retain_items < A2 ? retain_items : A2) : A2;
-        uint32_t a = 0, b2 = 0;
-        for (uint32_t i = 0; i < prefetch_items && (a < A2 || b2 < B2); ++i) {  // the order the next phase issues them in
-          int sidx;
-          uint32_t ch, bytes;
-          const uint8_t* src;
-          if (a < A2 && (b2 >= Bf2 || (uint64_t)a * Bf2 <= (uint64_t)b2 * A2)) {
-            src = locate(nxt, a < Rk2 ? A2 - Rk2 + a : a - Rk2, sidx, ch, bytes);
-            ++a;
-          } else src = locate(nn, b2++, sidx, ch, bytes);
-          if (bytes) asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-        }
-      }
+      setup_group<VE>(s_grp[(p + 2) % 3], segs, count, nxt.nseg ? nxt.end : count, lane);
     } else {
       // tails of both groups: elements past the last whole vector (CTA 0)
       if (bid == 0) {
@@ -767,17 +759,7 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
     }
     __syncthreads();
     if (s_fail) {
-      // A bounded wait ran out.  Copies already issued still write into this CTA's shared memory: wait (bounded
-      // again) for each of them before the CTA returns, then report through the sticky device flag.
-      if (tid == 0) {
-        g_pflag = 1;
-        for (uint32_t j = seq; j < s_issued; ++j) {
-          const int b = (int)(j % kPBufs);
-          if (!mbar_wait_bounded(full0 + 8 * b, (full_par >> b) & 1u)) break;
-          full_par ^= 1u << b;
-        }
-      }
-      __syncthreads();
+      fail_exit();
       return;
     }
     if (bid == 0 && tid < cur.nseg) cur.scale_absmax[tid][0] = cur.scale[tid];  // group p is done: publish its scale
@@ -790,7 +772,7 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
     ++nbar;
     if (tid == 0) CFB_TRACE(3);
     if (!grid_barrier_bounded(bar, nbar * G, bar_sleep_ns)) {
-      if (tid == 0) g_pflag = 1;
+      fail_exit();
       return;
     }
     if (tid < nxt.nseg) {
@@ -900,11 +882,11 @@ int32_t launch_persist_dt(const PSeg* table, int count, unsigned* bar, float qmi
   }
   const long long retain_mb = tunable(kTuneA1RetainMB);
   uint32_t retain_items = retain_mb >= 0 ? (uint32_t)(((size_t)retain_mb << 20) / ((size_t)kPItemBytes * sm_count())) : 0xffffffffu / 2;
-  long long pf = tunable(kTuneA1Prefetch), bs = tunable(kTuneA1BarSleep);
-  uint32_t prefetch_items = (uint32_t)(pf < 0 ? 0 : pf > 64 ? 64 : pf), bar_sleep_ns = (uint32_t)(bs < 0 ? 0 : bs > 1000 ? 1000 : bs);
+  const long long bs = tunable(kTuneA1BarSleep);
+  uint32_t bar_sleep_ns = (uint32_t)(bs < 0 ? 0 : bs > 1000 ? 1000 : bs);
   uint32_t tail_first = tunable(kTuneA1TailFirst) != 0;
   void* args[] = {(void*)&table, (void*)&count, (void*)&bar, (void*)&qmin, (void*)&qmax, (void*)&retain_items,
-                  (void*)&prefetch_items, (void*)&bar_sleep_ns, (void*)&tail_first};
+                  (void*)&bar_sleep_ns, (void*)&tail_first};
   CFB_CUDA(cudaLaunchCooperativeKernel((const void*)a1_persist_kernel<DT>, dim3((unsigned)sm_count()), dim3(kPThreads), args,
                                        (size_t)kPSmemBytes, st));
   return CFB200_OK;

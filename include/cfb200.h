@@ -51,8 +51,8 @@ const char* cfb200_version(void);
  * (L2 budget of a tensor group, default 64), "a1_retain_mb" (MB of a group's tail that the first
  * pass leaves in L2 at normal priority, default 60; negative = everything), "a1_tail_first" (1, default: the quantize
  * pass re-reads that tail before the lines that were let go; 0: oldest lines first), "a1_keep_mb",
- * "a1_demote", "a1_merge" (variants of the launch-per-group path), "a1_prefetch" (32 KB items per CTA that the cooperative
- * launch requests into L2 ahead of each grid barrier, default 0 = none), "a1_bar_sleep" (ns between polls of that barrier, default 0), "gemv_ring" (1, default: decode
+ * "a1_demote", "a1_merge" (variants of the launch-per-group path), "a1_bar_sleep" (ns between polls of the cooperative
+ * launch's grid barrier, default 0), "gemv_ring" (1, default: decode
  * shapes with 16 MB of packed weights or more use the shared-memory ring kernel; 0: never; n > 1: from n MB), "gemv_ring_rounds", "w4_split_k" (W4A16 prefill
  * with M <= 256: 0 = automatic split-K, 1 = never, n = at most n slices; changes the summation
  * order of the f32 accumulation and nothing else). */
