@@ -14,6 +14,7 @@
 #include <math.h>
 
 #include <mutex>
+#include <vector>
 #include <type_traits>
 
 #include "common.cuh"
@@ -629,8 +630,7 @@ void build_nf4_cells(Nf4Cell* cells) {
 }
 
 template <int DT, int EPL, int LPG, bool WIDE>
-__global__ void __launch_bounds__(kThreads)
-quant_nf4_kernel(const void* __restrict__ src, size_t n, uint8_t* __restrict__ codes, float* __restrict__ block_absmax) {
+__device__ __forceinline__ void quant_nf4_body(const void* __restrict__ src, size_t n, uint8_t* __restrict__ codes, float* __restrict__ block_absmax) {
   constexpr size_t G = (size_t)EPL * LPG;
   __shared__ Nf4Cell s_cells[32];
   if (threadIdx.x < 32) s_cells[threadIdx.x] = c_nf4_cells[threadIdx.x];
@@ -751,13 +751,37 @@ quant_nf4_kernel(const void* __restrict__ src, size_t n, uint8_t* __restrict__ c
 }
 
 // second level: absmax8 = clamp(round(a / s2), 0, 255), s2 = max(a)/255 per dq_block blocks
+template <int DT, int EPL, int LPG, bool WIDE>
 __global__ void __launch_bounds__(kThreads)
-nf4_double_quant_kernel(const float* __restrict__ block_absmax, size_t nblocks, size_t dq_block,
-                        uint8_t* __restrict__ absmax8, float* __restrict__ absmax2) {
+quant_nf4_kernel(const void* __restrict__ src, size_t n, uint8_t* __restrict__ codes, float* __restrict__ block_absmax) {
+  quant_nf4_body<DT, EPL, LPG, WIDE>(src, n, codes, block_absmax);
+}
+
+// One tensor of a list per blockIdx.y: the whole list in one launch, CTAs of the next tensor start as those of the
+// previous one finish.
+struct Nf4Seg {
+  const void* src;
+  size_t n;
+  uint8_t* codes;
+  float* block_absmax;  // inside the workspace
+  uint8_t* absmax8;
+  float* absmax2;
+  unsigned grid_x;      // CTAs this tensor has work for
+  unsigned pad;
+};
+template <int DT, int EPL, int LPG, bool WIDE>
+__global__ void __launch_bounds__(kThreads) quant_nf4_list_kernel(const Nf4Seg* __restrict__ segs) {
+  const Nf4Seg sg = segs[blockIdx.y];
+  if (blockIdx.x >= sg.grid_x) return;
+  quant_nf4_body<DT, EPL, LPG, WIDE>(sg.src, sg.n, sg.codes, sg.block_absmax);
+}
+
+__device__ __forceinline__ void nf4_double_quant_body(const float* __restrict__ block_absmax, size_t nblocks, size_t dq_block,
+                                                      uint8_t* __restrict__ absmax8, float* __restrict__ absmax2, unsigned stride) {
   __shared__ float s_part[kThreads / 32];
   __shared__ float s_max;
   const size_t nsb = (nblocks + dq_block - 1) / dq_block;
-  for (size_t sb = blockIdx.x; sb < nsb; sb += gridDim.x) {
+  for (size_t sb = blockIdx.x; sb < nsb; sb += stride) {
     const size_t b0 = sb * dq_block, b1 = b0 + dq_block < nblocks ? b0 + dq_block : nblocks;
     float m = 0.0f;
     for (size_t i = b0 + threadIdx.x; i < b1; i += kThreads) m = fmaxf(m, block_absmax[i]);
@@ -779,6 +803,18 @@ nf4_double_quant_kernel(const float* __restrict__ block_absmax, size_t nblocks, 
     }
     __syncthreads();
   }
+}
+
+__global__ void __launch_bounds__(kThreads)
+nf4_double_quant_kernel(const float* __restrict__ block_absmax, size_t nblocks, size_t dq_block,
+                        uint8_t* __restrict__ absmax8, float* __restrict__ absmax2) {
+  nf4_double_quant_body(block_absmax, nblocks, dq_block, absmax8, absmax2, gridDim.x);
+}
+__global__ void __launch_bounds__(kThreads) nf4_double_quant_list_kernel(const Nf4Seg* __restrict__ segs, size_t block, size_t dq_block) {
+  const Nf4Seg sg = segs[blockIdx.y];
+  const size_t nblocks = (sg.n + block - 1) / block;
+  if ((size_t)blockIdx.x * dq_block >= nblocks) return;  // uniform over the CTA: no super-block for it
+  nf4_double_quant_body(sg.block_absmax, nblocks, dq_block, sg.absmax8, sg.absmax2, gridDim.x);
 }
 
 // -------- launch helpers -------------------------------------------------------------------------
@@ -970,6 +1006,21 @@ extern "C" int32_t cfb200_quant_int4_asym(const void* src, int32_t src_dtype, si
   return CFB200_OK;
 }
 
+// The NF4 code table goes to constant memory once per device (not per host thread), on the first NF4 call there.
+static int32_t nf4_upload_cells(int dev, cudaStream_t st) {
+  static std::mutex cells_mutex;
+  static bool cells_ready[64];
+  std::lock_guard<std::mutex> lock(cells_mutex);
+  if (!cells_ready[dev]) {
+    Nf4Cell cells[32];
+    build_nf4_cells(cells);
+    CFB_CUDA(cudaMemcpyToSymbolAsync(c_nf4_cells, cells, sizeof cells, 0, cudaMemcpyHostToDevice, st));
+    CFB_CUDA(cudaStreamSynchronize(st));  // `cells` lives on this stack frame
+    cells_ready[dev] = true;
+  }
+  return CFB200_OK;
+}
+
 extern "C" size_t cfb200_quant_nf4_workspace_bytes(size_t n, size_t block) {
   if (block == 0) return 0;
   return ((n + block - 1) / block) * sizeof(float);
@@ -993,17 +1044,9 @@ extern "C" int32_t cfb200_quant_nf4(const void* src, int32_t src_dtype, size_t n
   int dev = 0;
   CFB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return set_error(CFB200_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
-  {  // the code table goes to constant memory once per device (not per host thread), on the first call there
-    static std::mutex cells_mutex;
-    static bool cells_ready[64];
-    std::lock_guard<std::mutex> lock(cells_mutex);
-    if (!cells_ready[dev]) {
-      Nf4Cell cells[32];
-      build_nf4_cells(cells);
-      CFB_CUDA(cudaMemcpyToSymbolAsync(c_nf4_cells, cells, sizeof cells, 0, cudaMemcpyHostToDevice, st));
-      CFB_CUDA(cudaStreamSynchronize(st));  // `cells` lives on this stack frame
-      cells_ready[dev] = true;
-    }
+  {
+    const int32_t rc_cells = nf4_upload_cells(dev, st);
+    if (rc_cells) return rc_cells;
   }
   float* am = reinterpret_cast<float*>(workspace);
   const bool wide = (reinterpret_cast<uintptr_t>(src) & 31) == 0;
@@ -1039,6 +1082,97 @@ extern "C" int32_t cfb200_quant_nf4(const void* src, int32_t src_dtype, size_t n
   const size_t nblocks = (n + block - 1) / block, nsb = (nblocks + dq_block - 1) / dq_block;
   size_t cap = (size_t)sm_count() * 8;
   nf4_double_quant_kernel<<<(int)(nsb < cap ? nsb : cap), kThreads, 0, st>>>(am, nblocks, dq_block, absmax8, absmax2);
+  CFB_LAUNCH_CHECK();
+  return CFB200_OK;
+}
+
+// A whole list of tensors in two launches (codes + block maxima, then the double quantisation): blockIdx.y picks
+// the tensor.  workspace = descriptor table (count entries, 256-byte aligned) + the f32 block maxima of every tensor.
+namespace {
+inline size_t nf4_align256(size_t x) { return (x + 255) & ~(size_t)255; }
+}
+extern "C" size_t cfb200_quant_nf4_tensors_workspace_bytes(int32_t count, const size_t* ns, size_t block) {
+  if (count <= 0 || !ns || block == 0) return 0;
+  size_t total = nf4_align256((size_t)count * sizeof(Nf4Seg));
+  for (int i = 0; i < count; ++i) total += nf4_align256(((ns[i] + block - 1) / block) * sizeof(float));
+  return total;
+}
+
+extern "C" int32_t cfb200_quant_nf4_tensors(int32_t count, const void* const* srcs, int32_t src_dtype, const size_t* ns, size_t block,
+                                            size_t dq_block, uint8_t* const* codes, uint8_t* const* absmax8, float* const* absmax2,
+                                            void* workspace, size_t workspace_bytes, void* stream) {
+  CFB_CHECK_ARG(count >= 0, "negative count");
+  if (count == 0) return CFB200_OK;
+  CFB_CHECK_ARG(count <= 65535, "at most 65535 tensors per call (got %d)", count);
+  CFB_CHECK_ARG(srcs && ns && codes && absmax8 && absmax2, "NULL argument");
+  CFB_CHECK_ARG(dtype_ok(src_dtype), "unknown src_dtype %d", src_dtype);
+  CFB_CHECK_ARG(block == 32 || block == 64 || block == 128 || block == 256, "block must be 32, 64, 128 or 256 (got %zu)", block);
+  CFB_CHECK_ARG(dq_block >= 1 && dq_block <= 1024, "dq_block must be in [1, 1024] (got %zu)", dq_block);
+  CFB_CHECK_ALIGNED(workspace, 256);
+  const size_t need = cfb200_quant_nf4_tensors_workspace_bytes(count, ns, block);
+  if (workspace == nullptr || workspace_bytes < need)
+    return set_error(CFB200_ERR_WORKSPACE, "quant_nf4_tensors needs %zu bytes of workspace, got %zu", need, workspace_bytes);
+  cudaStream_t st = (cudaStream_t)stream;
+  int dev = 0;
+  CFB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(CFB200_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::vector<Nf4Seg> table((size_t)count);
+  char* ws = reinterpret_cast<char*>(workspace);
+  size_t off = nf4_align256((size_t)count * sizeof(Nf4Seg));
+  bool wide = true;
+  size_t max_n = 0, max_nsb = 0;
+  for (int i = 0; i < count; ++i) {
+    CFB_CHECK_ARG(ns[i] == 0 || (srcs[i] && codes[i] && absmax8[i] && absmax2[i]), "tensor %d: NULL buffer", i);
+    CFB_CHECK_ALIGNED(srcs[i], 16);
+    CFB_CHECK_ALIGNED(codes[i], 16);
+    wide = wide && (reinterpret_cast<uintptr_t>(srcs[i]) & 31) == 0;
+    const size_t nb = (ns[i] + block - 1) / block;
+    table[i] = Nf4Seg{srcs[i], ns[i], codes[i], reinterpret_cast<float*>(ws + off), absmax8[i], absmax2[i], 0u, 0u};
+    off += nf4_align256(nb * sizeof(float));
+    max_n = ns[i] > max_n ? ns[i] : max_n;
+    const size_t nsb = (nb + dq_block - 1) / dq_block;
+    max_nsb = nsb > max_nsb ? nsb : max_nsb;
+  }
+  if (max_n == 0) return CFB200_OK;
+  int32_t rc = nf4_upload_cells(dev, st);
+  if (rc) return rc;
+  unsigned gx = 1;
+#define LAUNCH(DT, EPL, LPG)                                                                                    \
+  do {                                                                                                          \
+    gx = (unsigned)grid_for<EPL>(max_n);                                                                        \
+    for (int i = 0; i < count; ++i) table[i].grid_x = ns[i] ? (unsigned)grid_for<EPL>(ns[i]) : 0u;              \
+    CFB_CUDA(cudaMemcpyAsync(ws, table.data(), (size_t)count * sizeof(Nf4Seg), cudaMemcpyHostToDevice, st));    \
+    const dim3 grid(gx, (unsigned)count);                                                                       \
+    if (wide) quant_nf4_list_kernel<DT, EPL, LPG, true><<<grid, kThreads, 0, st>>>(reinterpret_cast<const Nf4Seg*>(ws));  \
+    else quant_nf4_list_kernel<DT, EPL, LPG, false><<<grid, kThreads, 0, st>>>(reinterpret_cast<const Nf4Seg*>(ws));     \
+  } while (0)
+  if (src_dtype == CFB200_F32) {
+    switch (block) {
+      case 32: LAUNCH(CFB200_F32, 8, 4); break;
+      case 64: LAUNCH(CFB200_F32, 8, 8); break;
+      case 128: LAUNCH(CFB200_F32, 8, 16); break;
+      default: LAUNCH(CFB200_F32, 8, 32); break;
+    }
+  } else if (src_dtype == CFB200_BF16) {
+    switch (block) {
+      case 32: LAUNCH(CFB200_BF16, 8, 4); break;
+      case 64: LAUNCH(CFB200_BF16, 16, 4); break;
+      case 128: LAUNCH(CFB200_BF16, 16, 8); break;
+      default: LAUNCH(CFB200_BF16, 16, 16); break;
+    }
+  } else {
+    switch (block) {
+      case 32: LAUNCH(CFB200_F16, 8, 4); break;
+      case 64: LAUNCH(CFB200_F16, 16, 4); break;
+      case 128: LAUNCH(CFB200_F16, 16, 8); break;
+      default: LAUNCH(CFB200_F16, 16, 16); break;
+    }
+  }
+#undef LAUNCH
+  CFB_LAUNCH_CHECK();
+  const size_t cap = (size_t)sm_count() * 8;
+  const dim3 g2((unsigned)(max_nsb < cap ? max_nsb : cap), (unsigned)count);
+  nf4_double_quant_list_kernel<<<g2, kThreads, 0, st>>>(reinterpret_cast<const Nf4Seg*>(ws), block, dq_block);
   CFB_LAUNCH_CHECK();
   return CFB200_OK;
 }

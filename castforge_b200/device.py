@@ -210,6 +210,31 @@ def quant_nf4(w: torch.Tensor, block: int = 64, dq_block: int = 256, workspace: 
     return codes, a8, a2
 
 
+def quant_nf4_tensors(ws: list[torch.Tensor], block: int = 64, dq_block: int = 256):
+    """E3 over a list of same-dtype device tensors in two launches.  Returns a list of (codes, absmax8, absmax2)."""
+    if not ws:
+        return []
+    ws = [_src(w) for w in ws]
+    dev, dt = ws[0].device, _dt(ws[0])
+    lib = load()
+    cnt = len(ws)
+    with torch.cuda.device(dev):
+        outs = []
+        for w in ws:
+            n = w.numel()
+            nb = (n + block - 1) // block
+            outs.append((torch.empty((n + 1) // 2, dtype=torch.uint8, device=dev), torch.empty(nb, dtype=torch.uint8, device=dev),
+                         torch.empty((nb + dq_block - 1) // dq_block, dtype=torch.float32, device=dev)))
+        ns = (ctypes.c_size_t * cnt)(*[w.numel() for w in ws])
+        arr = lambda xs: (ctypes.c_void_p * cnt)(*[x.data_ptr() for x in xs])
+        need = lib.cfb200_quant_nf4_tensors_workspace_bytes(cnt, ns, block)
+        wsb = torch.empty(need + 256, dtype=torch.uint8, device=dev)
+        wp = ctypes.c_void_p(wsb.data_ptr() + (-wsb.data_ptr()) % 256)
+        check(lib.cfb200_quant_nf4_tensors(cnt, arr(ws), dt, ns, block, dq_block, arr([o[0] for o in outs]), arr([o[1] for o in outs]),
+                                           arr([o[2] for o in outs]), wp, need, _stream(ws[0])))
+    return outs
+
+
 def cast_e4m3_rows(x: torch.Tensor):
     """E4 per-row (per-token) cast of [rows, cols] -> (codes u8, scales f32[rows])."""
     x = _src(x)

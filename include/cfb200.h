@@ -178,6 +178,15 @@ int32_t cfb200_quant_nf4(const void* src, int32_t src_dtype, size_t n, size_t bl
                          size_t dq_block, uint8_t* codes, uint8_t* absmax8, float* absmax2,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same over a list of tensors (a whole store) in two launches instead of two per tensor.  srcs / ns / codes /
+ * absmax8 / absmax2 are HOST arrays of `count` device pointers / element counts; results per tensor are identical to
+ * cfb200_quant_nf4.  workspace: 256-byte aligned, cfb200_quant_nf4_tensors_workspace_bytes(count, ns, block) bytes
+ * (a descriptor table, copied from host memory -- not callable under stream capture -- and the block maxima). */
+size_t cfb200_quant_nf4_tensors_workspace_bytes(int32_t count, const size_t* ns, size_t block);
+int32_t cfb200_quant_nf4_tensors(int32_t count, const void* const* srcs, int32_t src_dtype, const size_t* ns,
+                                 size_t block, size_t dq_block, uint8_t* const* codes, uint8_t* const* absmax8,
+                                 float* const* absmax2, void* workspace, size_t workspace_bytes, void* stream);
+
 /* NF4 for callers that must not allocate.  (No counterpart in the reference: CastForge's passes
  * allocate host vectors freely.)  Some hosts cannot give this library a workspace: an engine whose
  * memory manager has already claimed the whole device, so a cudaMalloc would fail; a serving loop

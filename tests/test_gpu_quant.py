@@ -462,6 +462,20 @@ def test_e3_nf4_dense_sweep_of_normalised_values(cuda_device, oracle):
     assert np.array_equal(codes.cpu().numpy(), c) and np.array_equal(a8.cpu().numpy(), b8)
 
 
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+@pytest.mark.parametrize("block", [32, 64, 256])
+def test_e3_nf4_list_equals_single_tensor_calls(cuda_device, dtype, block):
+    """cfb200_quant_nf4_tensors (one launch pair for a whole list): every tensor's codes, 8-bit maxima and second-level
+    scales EQUAL the single-tensor call's -- ragged sizes, a tensor shorter than one block, sizes that end inside a block."""
+    from castforge_b200 import device as cf
+    sizes = [64 * 256 * 3, 7, 64 * 1000 + 17, 1, 4096 * 130, 33, 64 * 256]
+    ws = [weights(n, n % 31 + block, DT[dtype]).to(cuda_device) for n in sizes]
+    got = cf.quant_nf4_tensors(ws, block, 256)
+    for w, (c, a8, a2) in zip(ws, got):
+        c1, b8, b2 = cf.quant_nf4(w, block, 256)
+        assert torch.equal(c, c1) and torch.equal(a8, b8) and torch.equal(a2.view(torch.int32), b2.view(torch.int32))
+
+
 def test_e3_workspace_too_small_is_rejected(cuda_device):
     from castforge_b200 import device as cf, CfbError
     w = weights(64 * 1000, 1, torch.bfloat16).to(cuda_device)
