@@ -86,8 +86,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // bounded wait; false = gave up (error recorded)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code, volatile int* s_abort) {
-  for (unsigned i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* error_flag, int code, volatile int* s_abort,
+                                          unsigned limit = kSpinLimit) {
+  for (unsigned i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *s_abort) return false;
   }
@@ -498,6 +499,20 @@ __global__ void bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, size_t n
   }
 }
 
+// The same staging pass with castforge.static_quantize (src/codegen/eval.rs:1369-1382) applied on the way: the f32 value
+// clamp(round(x / sc), +-qmax) * sc -- IEEE division, half-away rounding, separately rounded product, exactly as the
+// interpreter evaluates the op -- is what gets rounded to f16, so the activation matrix makes no extra trip through memory.
+template <bool F32IN>
+__global__ void static_quantize_to_f16_kernel(const void* __restrict__ x, size_t n, float sc, float qmax, __half* __restrict__ out) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    const float v = F32IN ? reinterpret_cast<const float*>(x)[i] : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(x)[i]);
+    float q = roundf(__fdiv_rn(v, sc));
+    q = (q != q) ? q : fminf(fmaxf(q, -qmax), qmax);
+    const float r = __fmul_rn(q, sc);
+    out[i] = __float2half_rn((r != r) ? r : fminf(fmaxf(r, -65504.0f), 65504.0f));
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------------------------
@@ -558,6 +573,34 @@ int32_t launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmAr
 }  // namespace cfb
 
 using namespace cfb;
+
+namespace cfb {
+namespace {
+// Self-test of the give-up path of the tensor-core kernels: the same bounded wait on a barrier that nothing completes,
+// with a short limit; the caller's error word receives the code, as it does from a kernel.
+__global__ void tc_wait_probe_kernel(int* error_flag, unsigned limit) {
+  __shared__ __align__(8) uint64_t s_bar;
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(smem_u32(&s_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_wait(smem_u32(&s_bar), 0u, error_flag, 7, &s_abort, limit);
+  }
+}
+}  // namespace
+int32_t tc_expired_wait_selftest(int32_t* observed) {
+  int* flag = nullptr;
+  CFB_CUDA(cudaMalloc(&flag, sizeof(int)));
+  cudaMemset(flag, 0, sizeof(int));
+  tc_wait_probe_kernel<<<1, 32>>>(flag, 1u << 12);
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaMemcpy(observed, flag, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaFree(flag);
+  if (e != cudaSuccess) return set_error(CFB200_ERR_CUDA, "wait probe failed: %s", cudaGetErrorString(e));
+  return CFB200_OK;
+}
+}  // namespace cfb
 
 extern "C" int32_t cfb200_gemm_fp8(const uint8_t* A, const float* a_scales, const uint8_t* W, float w_scale, size_t M, size_t N,
                                    size_t K, void* C, int32_t out_f32, int32_t* error_flag, void* stream) {
@@ -653,9 +696,12 @@ extern "C" size_t cfb200_gemm_w4a16_workspace_bytes(size_t M, size_t N, size_t K
   return w4_f16_bytes(M, K) + (S > 1 ? (size_t)S * M * N * 4 : 0);
 }
 
-extern "C" int32_t cfb200_gemm_w4a16(const void* A, const uint8_t* w_codes, const uint16_t* w_scales, const uint8_t* w_zps,
-                                     size_t M, size_t N, size_t K, size_t group, void* C, int32_t out_f32, void* workspace,
-                                     size_t workspace_bytes, int32_t* error_flag, void* stream) {
+namespace cfb {
+namespace {
+// a_mode: 0 = bf16 activations as they are; 1 / 2 = static_quantize(scale, bits) of bf16 / f32 activations in the staging pass
+int32_t gemm_w4a16_impl(const void* A, int a_mode, float a_scale, int a_bits, const uint8_t* w_codes, const uint16_t* w_scales,
+                        const uint8_t* w_zps, size_t M, size_t N, size_t K, size_t group, void* C, int32_t out_f32, void* workspace,
+                        size_t workspace_bytes, int32_t* error_flag, void* stream) {
   CFB_CHECK_ARG(A && w_codes && w_scales && w_zps && C, "NULL buffer");
   CFB_CHECK_ARG(M > 0 && N > 0 && K > 0 && K % 64 == 0, "W4A16 GEMM needs K a positive multiple of 64 (got %zu)", K);
   CFB_CHECK_ARG(group >= 64 && group % 64 == 0 && K % group == 0, "group must be a multiple of 64 dividing K (got %zu)", group);
@@ -670,8 +716,15 @@ extern "C" int32_t cfb200_gemm_w4a16(const void* A, const uint8_t* w_codes, cons
   // a device error (lost context) both times it ran.  kind::f16 takes ONE 16-bit format for both operands.
   const size_t n = M * K;
   size_t blocks = (n + 255) / 256, cap = (size_t)sm_count() * 16;
-  bf16_to_f16_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(A), n,
-                                                                             reinterpret_cast<__half*>(workspace));
+  const unsigned cgrid = (unsigned)(blocks < cap ? blocks : cap);
+  if (a_mode == 0) {
+    bf16_to_f16_kernel<<<cgrid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(A), n, reinterpret_cast<__half*>(workspace));
+  } else {
+    const float sc = a_scale > 0.0f ? a_scale : 1.0f / 127.0f;  // the interpreter's default for a missing scale attribute
+    const float qmax = a_bits == 4 ? 7.0f : 127.0f;
+    if (a_mode == 2) static_quantize_to_f16_kernel<true><<<cgrid, 256, 0, st>>>(A, n, sc, qmax, reinterpret_cast<__half*>(workspace));
+    else static_quantize_to_f16_kernel<false><<<cgrid, 256, 0, st>>>(A, n, sc, qmax, reinterpret_cast<__half*>(workspace));
+  }
   CFB_LAUNCH_CHECK();
   CUtensorMap tmA;
   int32_t rc = make_tmap(&tmA, workspace, 2, M, K, K, kBM);
@@ -690,4 +743,21 @@ extern "C" int32_t cfb200_gemm_w4a16(const void* A, const uint8_t* w_codes, cons
   split_k_reduce_kernel<<<(unsigned)((mn / 4 + 256) / 256), 256, 0, st>>>(g.partial, g.split_k, mn, C, out_f32);
   CFB_LAUNCH_CHECK();
   return CFB200_OK;
+}
+}  // namespace
+}  // namespace cfb
+
+extern "C" int32_t cfb200_gemm_w4a16(const void* A, const uint8_t* w_codes, const uint16_t* w_scales, const uint8_t* w_zps,
+                                     size_t M, size_t N, size_t K, size_t group, void* C, int32_t out_f32, void* workspace,
+                                     size_t workspace_bytes, int32_t* error_flag, void* stream) {
+  return gemm_w4a16_impl(A, 0, 0.0f, 8, w_codes, w_scales, w_zps, M, N, K, group, C, out_f32, workspace, workspace_bytes, error_flag, stream);
+}
+
+extern "C" int32_t cfb200_gemm_w4a16_static_quantize(const void* A, int32_t a_dtype, float a_scale, int32_t a_bits,
+                                                     const uint8_t* w_codes, const uint16_t* w_scales, const uint8_t* w_zps, size_t M,
+                                                     size_t N, size_t K, size_t group, void* C, int32_t out_f32, void* workspace,
+                                                     size_t workspace_bytes, int32_t* error_flag, void* stream) {
+  CFB_CHECK_ARG(a_dtype == CFB200_F32 || a_dtype == CFB200_BF16, "activations must be f32 or bf16 (got dtype %d)", a_dtype);
+  return gemm_w4a16_impl(A, a_dtype == CFB200_F32 ? 2 : 1, a_scale, a_bits, w_codes, w_scales, w_zps, M, N, K, group, C, out_f32, workspace,
+                         workspace_bytes, error_flag, stream);
 }

@@ -12,6 +12,11 @@
 // so the second read is served by L1 / L2) to emit the codes; the keys ride along in the same pass.  The two wider
 // scopes need every page before the first code can be written: absmax launch (shared-memory maxima per CTA, one
 // atomic per head per CTA), a one-block scale launch, then the same encode pass.
+#include <math.h>
+#include <string.h>
+
+#include <mutex>
+
 #include "common.cuh"
 
 namespace cfb {
@@ -252,7 +257,28 @@ kv_decode_kernel(const uint16_t* __restrict__ kb, const int8_t* __restrict__ vc,
   }
 }
 
-// E4M3FN slice codec: four elements per thread
+// E4M3FN slice codec: four elements per thread.
+// REF: reproduce the reference codec (src/passes/serving/mutable_loads.rs:367-410) where it departs from round-to-
+// nearest-even.  It takes the exponent as floor(log2f(|v|)); for a value a few ulp below a power of two 2^k the f32
+// logarithm rounds up to k, the mantissa term comes out slightly negative, `floor` gives -1, the round-up step adds one
+// to a mantissa that `as u8` clamped to 0, and the byte encodes 1.125 * 2^k instead of 2^k.  Which of the eight values
+// below each 2^k do this depends on the host's log2f, so the host evaluates it once (c_slip: bit t-1 of entry k+5 set =
+// 2^k * (1 - t * 2^-24) slips) and the kernel patches exactly those inputs.
+__constant__ uint8_t c_e4m3_slip[16];
+
+template <bool REF>
+__device__ __forceinline__ uint32_t e4m3_fix(uint32_t code, uint32_t bits) {
+  if constexpr (!REF) return code;
+  const uint32_t mant = bits & 0x7fffffu, ex = (bits >> 23) & 0xffu;
+  if (mant < 0x7ffff8u) return code;                    // not within 8 ulp below a power of two
+  const int k = (int)ex - 127 + 1;                      // the value lies just below 2^k
+  if (k < -5 || k > 8) return code;                     // below the normal range (other branch of the codec) or saturated
+  const uint32_t t = 0x800000u - mant;                  // 1..8
+  if (!((c_e4m3_slip[k + 5] >> (t - 1)) & 1u)) return code;
+  return (bits >> 24 & 0x80u) | (uint32_t)((k + 7) << 3) | 1u;   // k + 7 <= 15 and mantissa 1 < 7: never the NaN / saturation byte
+}
+
+template <bool REF>
 __global__ void __launch_bounds__(kThreadsKv) e4m3_slice_encode_kernel(const float* __restrict__ src, size_t n, uint8_t* __restrict__ out) {
   const size_t nq = n / 4;
   for (size_t i = (size_t)blockIdx.x * kThreadsKv + threadIdx.x; i < nq; i += (size_t)gridDim.x * kThreadsKv) {
@@ -260,13 +286,18 @@ __global__ void __launch_bounds__(kThreadsKv) e4m3_slice_encode_kernel(const flo
     unsigned short lo, hi;
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(__uint_as_float(r.y)), "f"(__uint_as_float(r.x)));
     asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(__uint_as_float(r.w)), "f"(__uint_as_float(r.z)));
-    st_stream4(out + i * 4, (uint32_t)lo | ((uint32_t)hi << 16));
+    uint32_t word = (uint32_t)lo | ((uint32_t)hi << 16);
+    if constexpr (REF) {
+      word = e4m3_fix<true>(word & 0xffu, r.x) | (e4m3_fix<true>((word >> 8) & 0xffu, r.y) << 8) |
+             (e4m3_fix<true>((word >> 16) & 0xffu, r.z) << 16) | (e4m3_fix<true>(word >> 24, r.w) << 24);
+    }
+    st_stream4(out + i * 4, word);
   }
   if (blockIdx.x == 0)
     for (size_t i = nq * 4 + threadIdx.x; i < n; i += kThreadsKv) {
       unsigned short pk;
       asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pk) : "f"(0.0f), "f"(src[i]));
-      out[i] = (uint8_t)(pk & 0xffu);
+      out[i] = (uint8_t)e4m3_fix<REF>(pk & 0xffu, __float_as_uint(src[i]));
     }
 }
 __device__ __forceinline__ float e4m3_value(uint32_t b) {  // mutable_loads.rs:413-429
@@ -396,7 +427,40 @@ extern "C" int32_t cfb200_e4m3_slice_encode(const float* src, size_t n, uint8_t*
   CFB_CHECK_ARG(src && codes, "NULL buffer");
   CFB_CHECK_ALIGNED(src, 16);
   CFB_CHECK_ALIGNED(codes, 4);
-  e4m3_slice_encode_kernel<<<kv_grid((n / 4 + kThreadsKv) / kThreadsKv), kThreadsKv, 0, (cudaStream_t)stream>>>(src, n, codes);
+  e4m3_slice_encode_kernel<false><<<kv_grid((n / 4 + kThreadsKv) / kThreadsKv), kThreadsKv, 0, (cudaStream_t)stream>>>(src, n, codes);
+  CFB_LAUNCH_CHECK();
+  return CFB200_OK;
+}
+
+// The reference codec bit for bit, its log2f binade slips included (see e4m3_fix).  The slip table is built from THIS
+// host's log2f on the first call on each device -- the function the reference's f32::log2 resolves to on the same host.
+extern "C" int32_t cfb200_e4m3_slice_encode_ref(const float* src, size_t n, uint8_t* codes, void* stream) {
+  if (n == 0) return CFB200_OK;
+  CFB_CHECK_ARG(src && codes, "NULL buffer");
+  CFB_CHECK_ALIGNED(src, 16);
+  CFB_CHECK_ALIGNED(codes, 4);
+  int dev = 0;
+  CFB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(CFB200_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  {
+    static std::mutex m;
+    static bool ready[64];
+    std::lock_guard<std::mutex> lock(m);
+    if (!ready[dev]) {
+      uint8_t slip[16] = {0};
+      for (int k = -5; k <= 8; ++k)
+        for (int t = 1; t <= 8; ++t) {
+          uint32_t bits = ((uint32_t)(k - 1 + 127) << 23) | (0x800000u - (uint32_t)t);
+          float x;
+          memcpy(&x, &bits, 4);
+          volatile float lg = log2f(x);  // volatile: evaluated by the library at run time, not folded by the compiler
+          if ((int)floorf(lg) == k) slip[k + 5] |= (uint8_t)(1u << (t - 1));
+        }
+      CFB_CUDA(cudaMemcpyToSymbol(c_e4m3_slip, slip, sizeof slip));
+      ready[dev] = true;
+    }
+  }
+  e4m3_slice_encode_kernel<true><<<kv_grid((n / 4 + kThreadsKv) / kThreadsKv), kThreadsKv, 0, (cudaStream_t)stream>>>(src, n, codes);
   CFB_LAUNCH_CHECK();
   return CFB200_OK;
 }

@@ -463,8 +463,8 @@ __device__ __forceinline__ bool grid_barrier_bounded(unsigned* ctr, unsigned tar
   return s_ok != 0;
 }
 
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity) {
-  for (unsigned it = 0; it < (1u << 22); ++it) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity, unsigned limit = 1u << 22) {
+  for (unsigned it = 0; it < limit; ++it) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                  : "=r"(ok) : "r"(mbar), "r"(parity) : "memory");
@@ -790,6 +790,18 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
   }
 }
 
+// Self-test of the give-up path: a wait on a barrier that nothing ever completes, with a short limit, reported the way
+// the persistent kernel reports it (the sticky device flag).  No memory is touched, nothing is left in flight.
+__global__ void a1_wait_probe_kernel(unsigned limit) {
+  __shared__ __align__(8) uint64_t s_bar;
+  const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&s_bar);
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    if (!mbar_wait_bounded(bar, 0u, limit)) g_pflag = 1;
+  }
+}
+
 void bounds_of(int32_t bits, float* qmin, float* qmax) {  // formats.rs:654-660
   if (bits == 4) { *qmin = -8.0f; *qmax = 7.0f; }
   else { *qmin = -128.0f; *qmax = 127.0f; }
@@ -975,6 +987,18 @@ extern "C" int32_t cfb200_debug_a1_trace(unsigned long long* host_out /* 3 * 200
   return CFB200_OK;
 }
 #endif
+
+namespace cfb {
+// Runs the probe, returns what cfb200_quant_sym_status reports afterwards, and clears the flag again.
+int32_t a1_expired_wait_selftest(int32_t* observed) {
+  a1_wait_probe_kernel<<<1, 32>>>(1u << 12);
+  CFB_LAUNCH_CHECK();
+  int32_t rc = cfb200_quant_sym_status(observed);
+  const int zero = 0;
+  CFB_CUDA(cudaMemcpyToSymbol(g_pflag, &zero, sizeof(int)));
+  return rc;
+}
+}  // namespace cfb
 
 extern "C" int32_t cfb200_quant_sym_apply(const void* src, int32_t src_dtype, size_t n, int32_t bits,
                                           const float* absmax, int8_t* codes, float* scale_absmax, void* stream) {

@@ -46,5 +46,13 @@ extern "C" int32_t cfb200_tune(const char* key, int64_t value) {
   return cfb::set_error(CFB200_ERR_INVALID, "unknown tunable '%s'", key ? key : "(null)");
 }
 
+extern "C" int32_t cfb200_selftest_expired_wait(int32_t which, int32_t* observed_host) {
+  if (!observed_host) return cfb::set_error(CFB200_ERR_INVALID, "NULL argument");
+  *observed_host = 0;
+  if (which == 0) return cfb::a1_expired_wait_selftest(observed_host);
+  if (which == 1) return cfb::tc_expired_wait_selftest(observed_host);
+  return cfb::set_error(CFB200_ERR_INVALID, "unknown self-test %d", which);
+}
+
 extern "C" const char* cfb200_last_error(void) { return cfb::t_last_error; }
 extern "C" const char* cfb200_version(void) { return "0.1.0"; }

@@ -421,6 +421,24 @@ def gemm_w4a16(a: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, zps: 
     return c
 
 
+def gemm_w4a16_static_quantize(a: torch.Tensor, a_scale: float, a_bits: int, codes: torch.Tensor, scales: torch.Tensor, zps: torch.Tensor,
+                               N: int, group: int = 128, out_f32: bool = False):
+    """gemm_w4a16 with castforge.static_quantize{scale, bits} applied to the f32 / bf16 activations in the staging pass."""
+    assert a.is_cuda and a.dtype in (torch.bfloat16, torch.float32)
+    a = a.contiguous()
+    M, K = a.shape
+    dev = a.device
+    with torch.cuda.device(dev):
+        c = torch.empty((M, N), dtype=torch.float32 if out_f32 else torch.bfloat16, device=dev)
+        flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        from ._lib import check as _chk
+        ws = torch.empty(load().cfb200_gemm_w4a16_workspace_bytes(M, N, K), dtype=torch.uint8, device=dev)
+        _chk(load().cfb200_gemm_w4a16_static_quantize(_p(a), _dt(a), float(a_scale), a_bits, _p(codes), _p(scales), _p(zps), M, N, K, group,
+                                                      _p(c), int(out_f32), _p(ws), ws.numel(), _p(flag), _stream(a)))
+        _check_flag(flag, "cfb200_gemm_w4a16_static_quantize")
+    return c
+
+
 def gemv_w4a16(a: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, zps: torch.Tensor, N: int, group: int = 128,
                out_f32: bool = False):
     """Decode-shape (M <= 16) W4A16 product; same operands as gemm_w4a16."""
@@ -545,6 +563,16 @@ def e4m3_slice_encode(x: torch.Tensor) -> torch.Tensor:
     with torch.cuda.device(x.device):
         out = torch.empty(x.numel(), dtype=torch.uint8, device=x.device)
         check(load().cfb200_e4m3_slice_encode(_p(x), x.numel(), _p(out), _stream(x)))
+    return out
+
+
+def e4m3_slice_encode_ref(x: torch.Tensor) -> torch.Tensor:
+    """The reference codec byte for byte (its log2f binade slips included)."""
+    x = _src(x)
+    assert x.dtype == torch.float32
+    with torch.cuda.device(x.device):
+        out = torch.empty(x.numel(), dtype=torch.uint8, device=x.device)
+        check(load().cfb200_e4m3_slice_encode_ref(_p(x), x.numel(), _p(out), _stream(x)))
     return out
 
 

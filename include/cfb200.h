@@ -101,6 +101,14 @@ int32_t cfb200_quant_sym_tensors(int32_t count, const void* const* srcs, int32_t
  * before it reports success.  (No counterpart in the reference: its pass cannot fail half-way.) */
 int32_t cfb200_quant_sym_status(int32_t* flag_host);
 
+/* Self-test of the give-up path that every spin-wait in the kernels has.  A one-warp kernel waits, with a limit of a
+ * few thousand polls, on a barrier that nothing completes, gives up and reports exactly as the real kernels do:
+ * which == 0: through the sticky flag of the cooperative A1 launch -- *observed_host receives what
+ * cfb200_quant_sym_status then reads (1), and the flag is cleared again; which == 1: through a caller error word as
+ * the tensor-core GEMMs use it -- *observed_host receives the code written there (7).  Touches no caller memory,
+ * leaves nothing in flight, runs in microseconds.  (which == 1 allocates and frees four bytes of device memory.) */
+int32_t cfb200_selftest_expired_wait(int32_t which, int32_t* observed_host);
+
 /* ---- A6: per-tensor fake quantization (QAT-STE) --------------------------------------------
  * Replaces run_qat_ste's arithmetic (src/passes/quantize/formats.rs:764-769): f32 in, f32 out,
  * out = clamp(round(v/scale)) * scale.  scale_absmax as above. */
@@ -277,6 +285,16 @@ int32_t cfb200_gemm_w4a16(const void* A, const uint8_t* w_codes, const uint16_t*
                           int32_t out_f32, void* workspace, size_t workspace_bytes,
                           int32_t* error_flag, void* stream);
 
+/* cfb200_gemm_w4a16 with castforge.static_quantize{scale, bits} on the activation operand (the `w8a8` rewrite of
+ * lower-mixed-precision, src/passes/quantize/formats.rs:541-611, evaluated by src/codegen/eval.rs:1369-1382) folded
+ * into the pass that stages the activations as f16: each value becomes clamp(round(x / scale), +-qmax) * scale in f32,
+ * with the interpreter's arithmetic, before it is rounded to f16 -- no separate launch, no extra copy of A.
+ * a_dtype: CFB200_F32 or CFB200_BF16; a_scale <= 0 means the interpreter's default 1/127; a_bits 4 -> qmax 7, else 127. */
+int32_t cfb200_gemm_w4a16_static_quantize(const void* A, int32_t a_dtype, float a_scale, int32_t a_bits,
+                                          const uint8_t* w_codes, const uint16_t* w_scales, const uint8_t* w_zps,
+                                          size_t M, size_t N, size_t K, size_t group, void* C, int32_t out_f32,
+                                          void* workspace, size_t workspace_bytes, int32_t* error_flag, void* stream);
+
 /* Decode shapes (1 <= M <= 16): the same W4A16 product, HBM-bound on the packed weights, which are
  * streamed once; dequantisation is exact (integer (q - zp) on the tensor cores, group scale
  * applied to the f32 group sum).  group must be 128, K % 128 == 0.  No workspace, one launch. */
@@ -413,6 +431,12 @@ int32_t cfb200_kv_decode_k16v8(const uint16_t* k_f16_bits, const int8_t* v_codes
                                size_t head_dim, int32_t scope, float* k_out, float* v_out, void* stream);
 int32_t cfb200_e4m3_slice_encode(const float* src, size_t n, uint8_t* codes, void* stream);
 int32_t cfb200_e4m3_slice_decode(const uint8_t* codes, size_t n, float* out, void* stream);
+/* The reference codec byte for byte.  f32_to_fp8_e4m3fn (mutable_loads.rs:391-393) takes its exponent from
+ * floor(log2f(|v|)); for the few f32 values within 8 ulp below a power of two 2^k whose logarithm rounds up to k it
+ * returns the byte of 1.125 * 2^k where round-to-nearest-even (cfb200_e4m3_slice_encode) gives 2^k.  This entry point
+ * reproduces those bytes too: which inputs slip is taken from the host's own log2f on the first call on each device
+ * (make that call outside stream capture).  Everything else is identical to cfb200_e4m3_slice_encode. */
+int32_t cfb200_e4m3_slice_encode_ref(const float* src, size_t n, uint8_t* codes, void* stream);
 
 /* ---- weight surgery upstream of quantize ----------------------------------------------------------
  * cfb200_merge_f32: merge_f32_tensors (src/passes/weights/merge.rs:396-440) over two f32 tensors of n

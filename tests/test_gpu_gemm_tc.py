@@ -91,6 +91,34 @@ def test_w4a16_prefill(cuda_device, oracle, shape):
     assert cb.dtype == torch.bfloat16 and rel_err(cb.float(), ref) < 3e-2       # + bf16 output rounding
 
 
+@pytest.mark.parametrize("adt", ["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(128, 256, 512), (300, 1024, 4096)])
+def test_w4a16_with_static_quantize_prologue(cuda_device, oracle, adt, shape):
+    """The `w8a8` execute path: castforge.static_quantize on the activation operand (eval.rs:1369-1382) folded into the
+    GEMM's staging pass.  Reference = f64 product of the interpreter's static_quantize output (bit-exact kernel of the same
+    op) with the dequantised weights; the bar is the tensor-core GEMM tolerance, 1e-2 x RMS."""
+    from castforge_b200 import device as cf
+    M, N, K = shape
+    g = torch.Generator(device=cuda_device).manual_seed(M + N)
+    w = torch.randn(N, K, device=cuda_device, generator=g) * 0.02
+    a32 = torch.randn(M, K, device=cuda_device, generator=g)
+    a32[:, ::97] *= 6                                     # some values beyond the clamp at +-127 * scale
+    a = a32 if adt == "f32" else a32.to(torch.bfloat16)
+    sc = 0.03125 * 1.1
+    codes, scales, zps = cf.quant_int4_asym(w.reshape(-1), 128)
+    got = cf.gemm_w4a16_static_quantize(a, sc, 8, codes, scales, zps, N, 128, out_f32=True)
+    asq = cf.static_quantize(a.float().reshape(-1), sc, 8).reshape(M, K)
+    assert float(asq.abs().max()) <= 127 * sc * (1 + 1e-6) and int(torch.unique(asq).numel()) <= 255
+    ng = K // 128
+    q = torch.stack([codes & 0xF, codes >> 4], 1).reshape(N, ng, 128).double()
+    zz = torch.stack([zps & 0xF, zps >> 4], 1).reshape(-1)[: N * ng].reshape(N, ng, 1).double()
+    wd = ((q - zz) * scales.double().reshape(N, ng, 1)).reshape(N, K)
+    assert rel_err(got, asq.double() @ wd.T) < 1e-2
+    # and it is what the unfused sequence (static_quantize launch, bf16 copy, GEMM) computes, up to that copy's rounding
+    unfused = cf.gemm_w4a16(asq.to(torch.bfloat16), codes, scales, zps, N, 128, out_f32=True)
+    assert rel_err(got, unfused.double()) < 1e-2
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("NK", [(4096, 4096), (264, 1024), (14336, 4096), (40, 128), (4096, 14336), (8200, 4096), (76040, 4096)])
 def test_w4a16_decode(cuda_device, oracle, M, NK):

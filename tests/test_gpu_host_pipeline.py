@@ -213,3 +213,17 @@ def test_a1_status_word_reads_zero_after_normal_runs(cuda_device):
     D.quant_sym_tensors([w[: 1 << 20], w[1 << 20: 3 << 20]], 8)
     flag = ctypes.c_int32(-1)
     assert cfb.load().cfb200_quant_sym_status(ctypes.byref(flag)) == 0 and flag.value == 0
+
+
+def test_bounded_waits_give_up_and_report(cuda_device):
+    """A wait that can never complete runs out after its limit and the host sees it: through the sticky A1 status word
+    (which the self-test clears again) and through a caller's error word as the tensor-core kernels use it.  The wait is
+    on a barrier in the probe kernel's own shared memory that nothing arrives at; no fault, no hang, microseconds."""
+    import ctypes
+    lib = cfb.load()
+    seen = ctypes.c_int32(-1)
+    assert lib.cfb200_selftest_expired_wait(0, ctypes.byref(seen)) == 0 and seen.value == 1
+    flag = ctypes.c_int32(-1)
+    assert lib.cfb200_quant_sym_status(ctypes.byref(flag)) == 0 and flag.value == 0      # cleared: later runs start clean
+    assert lib.cfb200_selftest_expired_wait(1, ctypes.byref(seen)) == 0 and seen.value == 7
+    assert lib.cfb200_selftest_expired_wait(9, ctypes.byref(seen)) == 1

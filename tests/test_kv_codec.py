@@ -166,6 +166,17 @@ def test_e4m3_slice_cuda(oracle, cuda_device):
     x = np.concatenate([x, (rng.standard_normal(100_003) * rng.choice([1e-3, 1.0, 200.0], 100_003)).astype(np.float32)])
     got = D.e4m3_slice_encode(torch.from_numpy(x).to(cuda_device)).cpu().numpy()
     assert np.array_equal(got, oracle.e4m3_slice_encode(x, 1))
+    # the reference-exact entry point: every power of two of the normal range with the 12 values below and above it
+    # (where the reference's floor(log2f) lands one binade high), on top of the set above
+    edge = []
+    for k in range(-7, 10):
+        b = np.float32(2.0 ** k).view(np.uint32)
+        edge += [np.uint32(int(b) + d) for d in range(-12, 13)]
+    xe = np.concatenate([x, np.array(edge, np.uint32).view(np.float32), -np.array(edge, np.uint32).view(np.float32)])
+    want_ref = oracle.e4m3_slice_encode(xe, 0)
+    got_ref = D.e4m3_slice_encode_ref(torch.from_numpy(xe).to(cuda_device)).cpu().numpy()
+    assert np.array_equal(got_ref, want_ref)
+    assert int((want_ref != oracle.e4m3_slice_encode(xe, 1)).sum()) > 0      # the set does contain slips
     codes = np.concatenate([np.arange(256, dtype=np.uint8), rng.integers(0, 256, 1001, dtype=np.uint8)])
     back = D.e4m3_slice_decode(torch.from_numpy(codes).to(cuda_device)).cpu().numpy()
     want = oracle.e4m3_slice_decode(codes)
