@@ -28,6 +28,9 @@
 struct cfb200_comm {
   ncclComm_t nccl = nullptr;
   int world = 1, rank = 0, device = 0;
+  // a side stream for small collectives that should not sit in the caller's stream between two kernels
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 
 namespace cfb {
@@ -183,6 +186,9 @@ extern "C" void cfb200_comm_free(cfb200_comm* comm) {
   if (!comm) return;
   const NcclApi* api;
   if (comm->nccl && nccl_api(&api) == CFB200_OK) api->CommDestroy(comm->nccl);
+  if (comm->ev_fork) cudaEventDestroy(comm->ev_fork);
+  if (comm->ev_join) cudaEventDestroy(comm->ev_join);
+  if (comm->side) cudaStreamDestroy(comm->side);
   delete comm;
 }
 
@@ -252,16 +258,28 @@ extern "C" int32_t cfb200_quant_sym_tensors_sharded(cfb200_comm* comm, int32_t c
     else rc = cudaMemsetAsync(scale_absmax + 2 * i, 0, 2 * sizeof(float), st) == cudaSuccess ? CFB200_OK : set_error(CFB200_ERR_CUDA, "cudaMemsetAsync failed");
     if (rc) return rc;
   }
-  if (!blocks.empty() && comm->world > 1) {
+  // The all-reduce runs on the communicator's side stream, forked from the caller's stream after the absmax kernels and
+  // joined before the first apply kernel, so that its latency (tens of microseconds for a few floats) passes under the
+  // list kernel of the whole tensors instead of between two kernels.
+  const bool exchange = !blocks.empty() && comm->world > 1;
+  if (exchange) {
     const NcclApi* api;
     rc = nccl_api(&api);
     if (rc) return rc;
+    if (!comm->side) {
+      CFB_CUDA(cudaStreamCreateWithFlags(&comm->side, cudaStreamNonBlocking));
+      CFB_CUDA(cudaEventCreateWithFlags(&comm->ev_fork, cudaEventDisableTiming));
+      CFB_CUDA(cudaEventCreateWithFlags(&comm->ev_join, cudaEventDisableTiming));
+    }
+    CFB_CUDA(cudaEventRecord(comm->ev_fork, st));
+    CFB_CUDA(cudaStreamWaitEvent(comm->side, comm->ev_fork, 0));
     CFB_NCCL(api, api->GroupStart());
     for (int i : blocks) {
-      ncclResult_t r = api->AllReduce(scale_absmax + 2 * i + 1, scale_absmax + 2 * i + 1, 1, ncclFloat32, ncclMax, comm->nccl, st);
+      ncclResult_t r = api->AllReduce(scale_absmax + 2 * i + 1, scale_absmax + 2 * i + 1, 1, ncclFloat32, ncclMax, comm->nccl, comm->side);
       if (r != ncclSuccess) { api->GroupEnd(); return set_error(CFB200_ERR_CUDA, "ncclAllReduce failed: %s", api->GetErrorString(r)); }
     }
     CFB_NCCL(api, api->GroupEnd());
+    CFB_CUDA(cudaEventRecord(comm->ev_join, comm->side));
   }
   // 2. whole tensors: the list kernel on every maximal run of consecutive whole tensors (results land in place);
   //    it runs while the all-reduce above is still in flight on the same stream order
@@ -275,6 +293,7 @@ extern "C" int32_t cfb200_quant_sym_tensors_sharded(cfb200_comm* comm, int32_t c
     k = e;
   }
   // 3. row blocks: codes from the global absmax
+  if (exchange) CFB_CUDA(cudaStreamWaitEvent(st, comm->ev_join, 0));
   for (int i : blocks) {
     rc = cfb200_quant_sym_apply(srcs[i], src_dtype, ns[i], bits, scale_absmax + 2 * i + 1, codes[i], scale_absmax + 2 * i, stream);
     if (rc) return rc;
