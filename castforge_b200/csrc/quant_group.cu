@@ -632,8 +632,11 @@ void build_nf4_cells(Nf4Cell* cells) {
 template <int DT, int EPL, int LPG, bool WIDE>
 __device__ __forceinline__ void quant_nf4_body(const void* __restrict__ src, size_t n, uint8_t* __restrict__ codes, float* __restrict__ block_absmax) {
   constexpr size_t G = (size_t)EPL * LPG;
-  __shared__ Nf4Cell s_cells[32];
-  if (threadIdx.x < 32) s_cells[threadIdx.x] = c_nf4_cells[threadIdx.x];
+  __shared__ Nf4Cell s_cells[32], s_rev[32];  // s_rev: the table back to front, for the fast path's index
+  if (threadIdx.x < 32) {
+    s_cells[threadIdx.x] = c_nf4_cells[threadIdx.x];
+    s_rev[31 - threadIdx.x] = c_nf4_cells[threadIdx.x];
+  }
   __syncthreads();
   const WarpWork w = warp_work<EPL>(n);
   const size_t nblocks = (n + G - 1) / G;
@@ -705,8 +708,12 @@ __device__ __forceinline__ void quant_nf4_body(const void* __restrict__ src, siz
 #pragma unroll
           for (int k = 7; k >= 0; --k) {
             const float x = __fmul_rn(f[8 * h + k], inv);
-            // |x| <= 1 + 2^-23, so the cell is in [0, 31]; NaN converts to cell 0, compares false -> code 0
-            const Nf4Cell e = s_cells[__float2int_rd(__fmaf_rn(x, 15.5f, 15.75f))];
+            // Cell index without a float -> int conversion: fma.ru(x, -62, 64 + 2^23) = 2^23 + ceil(4 (31 - e)) + 3 with
+            // e = 15.5 x + 15.75 exact, so bits [2, 7) of the result are 31 - floor(e), the index into the reversed table
+            // (checked on the host against the 15-comparison definition for every f32 in [-1 - 2^-22, 1 + 2^-22]).
+            // A NaN has all of those bits set -> reversed entry 31 = cell 0, compares false -> code 0.
+            const uint32_t tb = __float_as_uint(__fmaf_ru(x, -62.0f, 8388672.0f));
+            const Nf4Cell e = s_rev[(tb >> 2) & 31u];
             word = word * 16u + (uint32_t)(e.base + (x > e.thr ? 1 : 0));
           }
           words[h] = word;
