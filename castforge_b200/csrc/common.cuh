@@ -355,10 +355,18 @@ struct SelectState {
   unsigned long long bin_count;  // elements in the bin chosen by the latest pass; after the last pass: how many equal the threshold
   unsigned prefix;               // bits fixed so far (in place)
   unsigned mask;                 // which bits are fixed
+  unsigned ticket;               // CTAs that have delivered their histogram in the running pass (the last one scans)
+  unsigned pad;
 };
-// sub != NULL: select over src - sub, which the first pass also writes to diff_out (n floats, 16-byte aligned)
+// sub != NULL: select over src - sub, which the first pass also writes to diff_out (n floats, 16-byte aligned).
+// fast_ws / fast_bytes: optional extra workspace (select_fast_workspace_bytes(n)); with it, and for ranks in the top
+// 5 % of a tensor of a million elements or more, the tensor is read ONCE: a sample brackets the threshold, one pass counts
+// what lies above the bracket and collects what lies inside it, and the exact rank is found among those candidates.
+// The bracket is verified on the device (count above < k <= count above + candidates); if it does not hold, the
+// three full passes run instead, so the result is exact either way.
+size_t select_fast_workspace_bytes(size_t n);
 int32_t select_kth_abs_rank(const float* src, size_t n, unsigned long long k, float* thr_out, SelectState* state, cudaStream_t st,
-                            const float* sub = nullptr, float* diff_out = nullptr);
+                            const float* sub = nullptr, float* diff_out = nullptr, void* fast_ws = nullptr, size_t fast_bytes = 0);
 
 #endif  // __CUDACC__
 

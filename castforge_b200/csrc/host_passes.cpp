@@ -397,7 +397,7 @@ bool run_quantize_on_store(TensorStore& store, const QuantizeConfig& cfg, PassRe
     }
     if (!ok) continue;
     if (needs_f32) { p.out_bytes = n * 4; p.pieces.push_back({"", DType::F32, e.shape, 0, n * 4}); }
-    if (kind == kGroup) p.scratch_bytes = cfb200_select_kth_workspace_bytes();
+    if (kind == kGroup) p.scratch_bytes = cfb200_select_kth_workspace_bytes_for(n);
     todo.push_back(i);
     plans.push_back(std::move(p));
   }

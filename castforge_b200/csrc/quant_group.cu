@@ -185,18 +185,87 @@ __global__ void fakequant_group_generic_kernel(const float* __restrict__ src, si
 // -------- exact k-th largest |v| (radix select, passes of 11 + 10 + 10 bits, MSB first) --------
 __global__ void select_init_kernel(SelectState* s, unsigned long long k) {
   for (int i = threadIdx.x; i < kSelectBins; i += blockDim.x) s->hist[i] = 0;
-  if (threadIdx.x == 0) { s->k = k; s->prefix = 0; s->mask = 0; }
+  if (threadIdx.x == 0) { s->k = k; s->prefix = 0; s->mask = 0; s->ticket = 0; }
+}
+
+// One block of 256 threads: a thread owns nbins / 256 consecutive bins; suffix sums of the threads' totals (counted from
+// the top) and a short walk inside the owning thread's bins locate the bin holding rank k; its bits are fixed and
+// the bins are cleared.  Run by the LAST CTA of a histogram pass (ticket), so a pass is one launch.
+__device__ __forceinline__ void select_scan_block(SelectState* s, int shift, int nbits, float* thr_out, int last, unsigned base = 0u) {
+  __shared__ unsigned long long suf[256 + 1];
+  const int t = threadIdx.x, per = (1 << nbits) / 256;  // 4 or 8 bins per thread
+  unsigned long long bins[kSelectBins / 256];
+  unsigned long long mine = 0;
+  // written by other CTAs' atomics: read from L2 (ld.cg), all of a thread's loads in flight together
+#pragma unroll
+  for (int j = 0; j < kSelectBins / 256; ++j) bins[j] = j < per ? __ldcg(&s->hist[t * per + j]) : 0ull;
+#pragma unroll
+  for (int j = 0; j < kSelectBins / 256; ++j)
+    if (j < per) {
+      s->hist[t * per + j] = 0;
+      mine += bins[j];
+    }
+  suf[t] = mine;
+  if (t == 0) suf[256] = 0;
+  __syncthreads();
+  for (int o = 1; o < 256; o <<= 1) {  // suf[t] = sum of the bins of threads t .. 255
+    const unsigned long long add = (t + o < 256) ? suf[t + o] : 0ull;
+    __syncthreads();
+    suf[t] += add;
+    __syncthreads();
+  }
+  const unsigned long long k = __ldcg(&s->k);
+  __syncthreads();
+  // walking down from the top bin, the first bin whose suffix sum reaches k holds the rank; bin 0 if none does
+  const bool none = suf[0] < k;
+  if ((suf[t] >= k && suf[t + 1] < k) || (none && t == 0)) {
+    unsigned long long above = suf[t + 1];
+    int b = per - 1;
+    if (none) b = 0;
+    else
+      for (; b > 0; --b) {
+        if (above + bins[b] >= k) break;
+        above += bins[b];
+      }
+    s->k = none ? k - (suf[0] - bins[0]) : k - above;
+    s->prefix |= ((unsigned)(t * per + b)) << shift;
+    s->mask |= ((1u << nbits) - 1u) << shift;
+    s->bin_count = bins[b];
+    if (last) {
+      s->prefix += base;  // candidate passes work on offsets from the lower edge of the bracket
+      *thr_out = __uint_as_float(s->prefix);
+    }
+  }
+}
+
+// Tail of every histogram pass: the CTA's bins go to the global histogram, and the CTA that delivers last scans it.
+__device__ __forceinline__ void select_deliver_and_scan(const unsigned* sh, unsigned nbins, SelectState* s, int shift, int nbits,
+                                                        float* thr_out, int last, unsigned base = 0u) {
+  __shared__ int s_last;
+  for (unsigned i = threadIdx.x; i < nbins; i += kThreads)
+    if (sh[i]) atomicAdd(&s->hist[i], (unsigned long long)sh[i]);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&s->ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (s_last) {
+    __threadfence();
+    select_scan_block(s, shift, nbits, thr_out, last, base);
+    __syncthreads();
+    if (threadIdx.x == 0) s->ticket = 0;
+  }
 }
 
 __global__ void __launch_bounds__(kThreads)
 select_hist_kernel(const float* __restrict__ src, const float* __restrict__ sub, float* __restrict__ diff_out, size_t n, int shift,
-                   int nbits, SelectState* __restrict__ s) {
+                   int nbits, SelectState* __restrict__ s, float* thr_out, int last, const int* skip_if_set) {
   // sub != NULL: the values are src - sub, which this pass also writes to diff_out (the later passes read them there)
   __shared__ unsigned sh[kSelectBins];
+  if (skip_if_set && __ldcg(skip_if_set)) return;  // the single-pass path already found the answer
   const unsigned nbins = 1u << nbits, bin_mask = nbins - 1u;
   for (unsigned i = threadIdx.x; i < nbins; i += kThreads) sh[i] = 0;
   __syncthreads();
-  const unsigned prefix = s->prefix, mask = s->mask;
+  const unsigned prefix = __ldcg(&s->prefix), mask = __ldcg(&s->mask);
   auto add = [&](unsigned bits) {
     unsigned key = bits & 0x7fffffffu;  // |v| under IEEE total order; NaN above +inf
     if ((key & mask) == prefix) atomicAdd(&sh[(key >> shift) & bin_mask], 1u);
@@ -222,55 +291,217 @@ select_hist_kernel(const float* __restrict__ src, const float* __restrict__ sub,
     add(__float_as_uint(v));
   }
   __syncthreads();
-  for (unsigned i = threadIdx.x; i < nbins; i += kThreads)
-    if (sh[i]) atomicAdd(&s->hist[i], (unsigned long long)sh[i]);
+  select_deliver_and_scan(sh, nbins, s, shift, nbits, thr_out, last);
 }
 
-// one block of 256 threads: a thread owns nbins / 256 consecutive bins; suffix sums of the threads' totals (counted from
-// the top) and a short walk inside the owning thread's bins locate the bin holding rank k; its bits are fixed and
-// the bins are cleared
-__global__ void __launch_bounds__(256) select_scan_kernel(SelectState* s, int shift, int nbits, float* thr_out, int last) {
-  __shared__ unsigned long long suf[256 + 1];
-  const int t = threadIdx.x, per = (1 << nbits) / 256;  // 4 or 8 bins per thread
-  unsigned long long bins[kSelectBins / 256];
+// ---- single-pass path: sample -> bracket -> one full pass -> exact rank among the candidates -----------------------
+constexpr int kSampleBits = 13, kSampleBins = 1 << kSampleBits, kSampleShift = 31 - kSampleBits;  // top 13 bits of |v|
+constexpr int kFastStage = 2048;       // candidates a CTA of the bracket pass can hold in shared memory
+constexpr unsigned kFastSpanBits = 21; // the bracket must span fewer than 2^21 keys: two radix passes (11 + 10 bits) over the offsets
+constexpr size_t kSampleCount = 1u << 18;
+struct SelectFast {
+  unsigned lo_key, hi_key;           // candidates: lo_key <= key < hi_key
+  unsigned long long cnt_above;      // keys >= hi_key
+  unsigned long long cand_total;     // candidates written to the dense buffer
+  int fast_ok, overflow;
+  unsigned ticket, pad;
+  unsigned sample_hist[kSampleBins];
+};
+
+__device__ __forceinline__ unsigned abs_key(float v) { return __float_as_uint(v) & 0x7fffffffu; }
+
+// A spread-out sample of the tensor, binned on the top 14 magnitude bits; the last CTA turns the two sample ranks that
+// bracket rank k (6 standard deviations of the sample count on either side) into a key range.
+__global__ void __launch_bounds__(kThreads)
+select_sample_kernel(const float* __restrict__ src, const float* __restrict__ sub, size_t n, size_t samples, unsigned long long k,
+                     SelectFast* __restrict__ f, SelectState* __restrict__ s) {
+  __shared__ unsigned sh[kSampleBins];  // 32 KB: the CTA's own histogram, delivered once
+  for (int i = threadIdx.x; i < kSampleBins; i += kThreads) sh[i] = 0;
+  __syncthreads();
+  const size_t stride = n / samples;  // >= 4: the path is only taken for large tensors
+  const size_t step = (size_t)gridDim.x * kThreads;
+  for (size_t j0 = (size_t)blockIdx.x * kThreads + threadIdx.x; j0 < samples; j0 += 4 * step) {
+    float v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {  // four independent loads in flight per thread
+      const size_t j = j0 + u * step;
+      const size_t pos = j * stride + (size_t)((unsigned)(j * 2654435761u) % (unsigned)(stride < 0xffffffffu ? stride : 0xffffffffu));
+      v[u] = j < samples ? __ldg(src + pos) : 0.0f;
+      if (sub && j < samples) v[u] = __fsub_rn(v[u], __ldg(sub + pos));
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (j0 + u * step < samples) atomicAdd(&sh[abs_key(v[u]) >> kSampleShift], 1u);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kSampleBins; i += kThreads)
+    if (sh[i]) atomicAdd(&f->sample_hist[i], sh[i]);
+  __shared__ int s_last;
+  __shared__ unsigned long long suf[kThreads + 1];
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&f->ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  constexpr int per = kSampleBins / kThreads;  // 64 consecutive bins per thread
+  const int t = threadIdx.x;
+  unsigned bins[per];
   unsigned long long mine = 0;
 #pragma unroll
-  for (int j = 0; j < kSelectBins / 256; ++j) {
-    bins[j] = 0;
-    if (j < per) {
-      bins[j] = s->hist[t * per + j];
-      s->hist[t * per + j] = 0;
-      mine += bins[j];
-    }
-  }
+  for (int j = 0; j < per; ++j) bins[j] = __ldcg(&f->sample_hist[t * per + j]);
+#pragma unroll
+  for (int j = 0; j < per; ++j) mine += bins[j];
   suf[t] = mine;
-  if (t == 0) suf[256] = 0;
+  if (t == 0) suf[kThreads] = 0;
   __syncthreads();
-  for (int o = 1; o < 256; o <<= 1) {  // suf[t] = sum of the bins of threads t .. 255
-    const unsigned long long add = (t + o < 256) ? suf[t + o] : 0ull;
+  for (int o = 1; o < kThreads; o <<= 1) {
+    const unsigned long long add = (t + o < kThreads) ? suf[t + o] : 0ull;
     __syncthreads();
     suf[t] += add;
     __syncthreads();
   }
-  const unsigned long long k = s->k;
-  __syncthreads();
-  // walking down from the top bin, the first bin whose suffix sum reaches k holds the rank; bin 0 if none does
-  const bool none = suf[0] < k;
-  if ((suf[t] >= k && suf[t + 1] < k) || (none && t == 0)) {
-    unsigned long long above = suf[t + 1];
-    int b = per - 1;
-    if (none) b = 0;
-    else
-      for (; b > 0; --b) {
-        if (above + bins[b] >= k) break;
-        above += bins[b];
-      }
-    s->k = none ? k - (suf[0] - bins[0]) : k - above;
-    s->prefix |= ((unsigned)(t * per + b)) << shift;
-    s->mask |= ((1u << nbits) - 1u) << shift;
-    s->bin_count = bins[b];
-    if (last) *thr_out = __uint_as_float(s->prefix);
+  const double ks = (double)k * (double)samples / (double)n;
+  const double m = 6.0 * sqrt(ks > 1.0 ? ks : 1.0) + 8.0;
+  const double r_hi = ks - m, r_lo = ks + m;
+  if (t == 0) {
+    if (r_hi < 1.0) f->hi_key = 0x80000000u;   // nothing is assumed to lie above the bracket
+    if (r_lo > (double)suf[0]) f->lo_key = 0u;
+    f->ticket = 0;
+    s->k = k;  // the select state was cleared by the memset that precedes this launch; only the rank is not zero
   }
+  // bin of sample rank r (counted from the top): suffix(bin) >= r > suffix(bin + 1)
+  auto locate = [&](double r, bool upper_edge) {
+    const unsigned long long rr = (unsigned long long)ceil(r);
+    if (suf[t] >= rr && suf[t + 1] < rr) {
+      unsigned long long above = suf[t + 1];
+      int b = per - 1;
+      bool found = false;
+#pragma unroll
+      for (int j = per - 1; j > 0; --j) {  // registers: unrolled, no dependent memory trips
+        if (!found) {
+          if (above + bins[j] >= rr) { b = j; found = true; }
+          else above += bins[j];
+        }
+      }
+      if (!found) b = 0;
+      const unsigned bin = (unsigned)(t * per + b);
+      if (upper_edge) f->hi_key = (bin + 1u) << kSampleShift;  // bin 16383 -> 0x80000000
+      else f->lo_key = bin << kSampleShift;
+    }
+  };
+  if (r_hi >= 1.0) locate(r_hi, true);
+  if (r_lo <= (double)suf[0]) locate(r_lo, false);
+}
+
+// The one full pass: keys at or above the bracket are counted, keys inside it are collected in shared memory and
+// appended to the dense candidate buffer with one reservation per CTA.  The last CTA checks that rank k falls among the
+// candidates.
+__global__ void __launch_bounds__(kThreads)
+select_bracket_kernel(const float* __restrict__ src, const float* __restrict__ sub, float* __restrict__ diff_out, size_t n,
+                      unsigned long long k, SelectFast* __restrict__ f, unsigned* __restrict__ cand, unsigned long long cand_cap,
+                      SelectState* __restrict__ s) {
+  __shared__ unsigned s_stage[kFastStage];
+  __shared__ unsigned s_cnt;
+  __shared__ unsigned long long s_base;
+  __shared__ int s_last;
+  __shared__ unsigned long long s_sum[kThreads / 32];
+  if (threadIdx.x == 0) s_cnt = 0;
+  __syncthreads();
+  const unsigned lo = f->lo_key, hi = f->hi_key;
+  unsigned above = 0;
+  auto visit = [&](unsigned bits) {
+    const unsigned key = bits & 0x7fffffffu;
+    if (key >= hi) ++above;
+    else if (key >= lo) {
+      const unsigned slot = atomicAdd(&s_cnt, 1u);
+      if (slot < (unsigned)kFastStage) s_stage[slot] = key - lo;  // offset from the lower edge
+    }
+  };
+  const size_t nvec = n / 4;
+  const uint4* p = reinterpret_cast<const uint4*>(src);
+  const size_t gstep = (size_t)gridDim.x * kThreads;
+  size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  if (!sub) {  // plain tensor: four loads in flight per thread
+    for (; i + 3 * gstep < nvec; i += 4 * gstep) {
+      const uint4 r0 = ld_stream16(p + i), r1 = ld_stream16(p + i + gstep), r2 = ld_stream16(p + i + 2 * gstep), r3 = ld_stream16(p + i + 3 * gstep);
+      visit(r0.x); visit(r0.y); visit(r0.z); visit(r0.w);
+      visit(r1.x); visit(r1.y); visit(r1.z); visit(r1.w);
+      visit(r2.x); visit(r2.y); visit(r2.z); visit(r2.w);
+      visit(r3.x); visit(r3.y); visit(r3.z); visit(r3.w);
+    }
+  }
+  for (; i < nvec; i += gstep) {
+    uint4 r = ld_stream16(p + i);
+    if (sub) {
+      const uint4 q = ld_stream16(reinterpret_cast<const uint4*>(sub) + i);
+      r.x = __float_as_uint(__fsub_rn(__uint_as_float(r.x), __uint_as_float(q.x)));
+      r.y = __float_as_uint(__fsub_rn(__uint_as_float(r.y), __uint_as_float(q.y)));
+      r.z = __float_as_uint(__fsub_rn(__uint_as_float(r.z), __uint_as_float(q.z)));
+      r.w = __float_as_uint(__fsub_rn(__uint_as_float(r.w), __uint_as_float(q.w)));
+      reinterpret_cast<uint4*>(diff_out)[i] = r;
+    }
+    visit(r.x); visit(r.y); visit(r.z); visit(r.w);
+  }
+  if (blockIdx.x == 0 && threadIdx.x < (unsigned)(n - nvec * 4)) {
+    const size_t i = nvec * 4 + threadIdx.x;
+    float v = src[i];
+    if (sub) { v = __fsub_rn(v, sub[i]); diff_out[i] = v; }
+    visit(__float_as_uint(v));
+  }
+  unsigned long long a = above;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(kFullMask, a, o);
+  if ((threadIdx.x & 31) == 0) s_sum[threadIdx.x >> 5] = a;
+  __syncthreads();
+  const unsigned cnt = s_cnt < (unsigned)kFastStage ? s_cnt : (unsigned)kFastStage;
+  if (threadIdx.x == 0) {
+    unsigned long long tot = 0;
+    for (int w = 0; w < kThreads / 32; ++w) tot += s_sum[w];
+    if (tot) atomicAdd(&f->cnt_above, tot);
+    if (s_cnt > (unsigned)kFastStage) atomicExch(&f->overflow, 1);
+    s_base = cnt ? atomicAdd(&f->cand_total, (unsigned long long)cnt) : 0ull;
+  }
+  __syncthreads();
+  const unsigned long long base = s_base;
+  if (base + cnt <= cand_cap) {
+    for (unsigned i = threadIdx.x; i < cnt; i += kThreads) cand[base + i] = s_stage[i];
+  } else if (threadIdx.x == 0) atomicExch(&f->overflow, 1);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicAdd(&f->ticket, 1u) == gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (threadIdx.x == 0) {  // last CTA: does rank k fall among the candidates?
+    const unsigned long long total = *reinterpret_cast<volatile unsigned long long*>(&f->cand_total);
+    const unsigned long long ab = *reinterpret_cast<volatile unsigned long long*>(&f->cnt_above);
+    const bool ok = !*reinterpret_cast<volatile int*>(&f->overflow) && ab < k && k <= ab + total && hi - lo <= (1u << kFastSpanBits);
+    f->fast_ok = ok ? 1 : 0;
+    s->k = ok ? k - ab : k;   // rank among the candidates, or the untouched rank for the three full passes
+    f->ticket = 0;
+  }
+}
+
+// The radix passes over the dense candidate buffer (its length is on the device).  The candidates share their top bits,
+// so they are stored as offsets from the lower edge of the bracket (< 2^21) and two passes, 11 + 10 bits, resolve them.
+__global__ void __launch_bounds__(kThreads)
+select_hist_cand_kernel(const unsigned* __restrict__ cand, const SelectFast* __restrict__ f, int shift, int nbits,
+                        SelectState* __restrict__ s, float* thr_out, int last) {
+  __shared__ unsigned sh[kSelectBins];
+  const int fast_ok = __ldcg(&f->fast_ok);
+  const unsigned prefix = __ldcg(&s->prefix), mask = __ldcg(&s->mask), base = __ldcg(&f->lo_key);
+  const size_t total = (size_t)__ldcg(&f->cand_total);
+  if (!fast_ok) return;
+  const unsigned nbins = 1u << nbits, bin_mask = nbins - 1u;
+  for (unsigned i = threadIdx.x; i < nbins; i += kThreads) sh[i] = 0;
+  __syncthreads();
+  for (size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x; i < total; i += (size_t)gridDim.x * kThreads) {
+    const unsigned key = cand[i];
+    if ((key & mask) == prefix) atomicAdd(&sh[(key >> shift) & bin_mask], 1u);
+  }
+  __syncthreads();
+  select_deliver_and_scan(sh, nbins, s, shift, nbits, thr_out, last, base);
 }
 
 // -------- A3 -----------------------------------------------------------------------------------
@@ -866,18 +1097,46 @@ void bounds_of(int32_t bits, float* qmin, float* qmax) {
 using namespace cfb;
 
 namespace cfb {
+size_t select_fast_workspace_bytes(size_t n) {
+  const size_t cand = n / 64 > (size_t)(1u << 18) ? n / 64 : (size_t)(1u << 18);
+  return ((sizeof(SelectFast) + 255) & ~(size_t)255) + cand * sizeof(unsigned) + 256;
+}
+
 // k-th largest |v| (1 <= k <= n) into thr_out; `state` keeps the rank inside the elements equal to it and their count
 int32_t select_kth_abs_rank(const float* src, size_t n, unsigned long long k, float* thr_out, SelectState* state, cudaStream_t st,
-                            const float* sub, float* diff_out) {
-  select_init_kernel<<<1, 256, 0, st>>>(state, k);
+                            const float* sub, float* diff_out, void* fast_ws, size_t fast_bytes) {
   size_t blocks = (n / 4 + kThreads - 1) / kThreads, cap = (size_t)sm_count() * 8;
   int grid = (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
   // the 31 magnitude bits in three passes: 11 + 10 + 10
   static const int kShift[3] = {20, 10, 0}, kBits[3] = {11, 10, 10};
+  const int* skip = nullptr;
+  const float* pass_src = src;
+  const float* pass_sub = sub;
+  // single-pass path: large tensors, ranks in the top 5 %, enough workspace
+  // (a CTA of the bracket pass stages its candidates in shared memory: about 0.5 % of its share of the tensor must fit)
+  const bool fast = fast_ws && n >= ((size_t)1 << 20) && k * 20 <= n && fast_bytes >= select_fast_workspace_bytes(n) &&
+                    n / (size_t)grid / 200 <= (size_t)kFastStage / 4 && (reinterpret_cast<uintptr_t>(fast_ws) & 255) == 0;
+  if (fast) CFB_CUDA(cudaMemsetAsync(state, 0, sizeof(SelectState), st));
+  else select_init_kernel<<<1, 256, 0, st>>>(state, k);
+  if (fast) {
+    SelectFast* f = reinterpret_cast<SelectFast*>(fast_ws);
+    unsigned* cand = reinterpret_cast<unsigned*>(reinterpret_cast<char*>(fast_ws) + ((sizeof(SelectFast) + 255) & ~(size_t)255));
+    const size_t cand_cap = n / 64 > (size_t)(1u << 18) ? n / 64 : (size_t)(1u << 18);
+    CFB_CUDA(cudaMemsetAsync(f, 0, sizeof(SelectFast), st));
+    const size_t samples = kSampleCount < n / 4 ? kSampleCount : n / 4;
+    select_sample_kernel<<<256, kThreads, 0, st>>>(src, sub, n, samples, k, f, state);
+    select_bracket_kernel<<<grid, kThreads, 0, st>>>(src, sub, diff_out, n, k, f, cand, (unsigned long long)cand_cap, state);
+    select_hist_cand_kernel<<<32, kThreads, 0, st>>>(cand, f, 10, 11, state, thr_out, 0);
+    select_hist_cand_kernel<<<32, kThreads, 0, st>>>(cand, f, 0, 10, state, thr_out, 1);
+    skip = &f->fast_ok;  // the full passes below only run if the bracket did not hold
+    if (sub) { pass_src = diff_out; pass_sub = nullptr; }  // the bracket pass has written the differences already
+  }
   for (int pass = 0; pass < 3; ++pass) {
-    if (pass == 0 || sub == nullptr) select_hist_kernel<<<grid, kThreads, 0, st>>>(src, sub, diff_out, n, kShift[pass], kBits[pass], state);
-    else select_hist_kernel<<<grid, kThreads, 0, st>>>(diff_out, nullptr, nullptr, n, kShift[pass], kBits[pass], state);
-    select_scan_kernel<<<1, 256, 0, st>>>(state, kShift[pass], kBits[pass], thr_out, pass == 2);
+    if (pass == 0 || pass_sub == nullptr)
+      select_hist_kernel<<<grid, kThreads, 0, st>>>(pass_src, pass == 0 ? pass_sub : nullptr, diff_out, n, kShift[pass], kBits[pass], state,
+                                                     thr_out, pass == 2, skip);
+    else
+      select_hist_kernel<<<grid, kThreads, 0, st>>>(diff_out, nullptr, nullptr, n, kShift[pass], kBits[pass], state, thr_out, pass == 2, skip);
   }
   CFB_LAUNCH_CHECK();
   return CFB200_OK;
@@ -885,6 +1144,9 @@ int32_t select_kth_abs_rank(const float* src, size_t n, unsigned long long k, fl
 }  // namespace cfb
 
 extern "C" size_t cfb200_select_kth_workspace_bytes(void) { return sizeof(SelectState); }
+extern "C" size_t cfb200_select_kth_workspace_bytes_for(size_t n) {
+  return ((sizeof(SelectState) + 255) & ~(size_t)255) + select_fast_workspace_bytes(n);
+}
 
 extern "C" int32_t cfb200_select_kth_abs(const float* src, size_t n, float salient_ratio, float* thr_out,
                                          uint64_t* k_host, void* workspace, size_t workspace_bytes, void* stream) {
@@ -906,7 +1168,16 @@ extern "C" int32_t cfb200_select_kth_abs(const float* src, size_t n, float salie
     CFB_CUDA(cudaMemsetAsync(thr_out, 0, sizeof(float), st));
     return CFB200_OK;
   }
-  return select_kth_abs_rank(src, n, (unsigned long long)k, thr_out, reinterpret_cast<SelectState*>(workspace), st);
+  // a workspace of cfb200_select_kth_workspace_bytes_for(n) bytes enables the single-pass path
+  const size_t head = (sizeof(SelectState) + 255) & ~(size_t)255;
+  void* fast = nullptr;
+  size_t fast_bytes = 0;
+  if (workspace_bytes >= cfb200_select_kth_workspace_bytes_for(n) && (reinterpret_cast<uintptr_t>(workspace) & 255) == 0) {
+    fast = reinterpret_cast<char*>(workspace) + head;
+    fast_bytes = workspace_bytes - head;
+  }
+  return select_kth_abs_rank(src, n, (unsigned long long)k, thr_out, reinterpret_cast<SelectState*>(workspace), st, nullptr, nullptr, fast,
+                             fast_bytes);
 }
 
 extern "C" int32_t cfb200_fakequant_group(const float* src, size_t n, int32_t bits, size_t group_size,

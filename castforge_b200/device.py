@@ -128,13 +128,15 @@ def quant_per_channel(w: torch.Tensor, bits: int = 8):
     return codes, scales
 
 
-def select_kth_abs(w: torch.Tensor, salient_ratio: float):
-    """A2 threshold: (thr f32[1] on device, k)."""
+def select_kth_abs(w: torch.Tensor, salient_ratio: float, single_pass: bool = True):
+    """A2 threshold: (thr f32[1] on device, k).  single_pass: give the call the larger workspace that lets it read a
+    large tensor once (sample, bracket, candidates) instead of three times; the result is the same exact value."""
     w = _src(w)
     assert w.dtype == torch.float32
     lib = load()
     with torch.cuda.device(w.device):
-        ws = torch.empty(lib.cfb200_select_kth_workspace_bytes(), dtype=torch.uint8, device=w.device)
+        nbytes = lib.cfb200_select_kth_workspace_bytes_for(w.numel()) if single_pass else lib.cfb200_select_kth_workspace_bytes()
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=w.device)
         thr = torch.empty(1, dtype=torch.float32, device=w.device)
         k = ctypes.c_uint64(0)
         check(lib.cfb200_select_kth_abs(_p(w), w.numel(), salient_ratio, _p(thr), ctypes.byref(k), _p(ws), ws.numel(), _stream(w)))

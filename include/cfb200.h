@@ -135,10 +135,15 @@ int32_t cfb200_quant_per_channel(const void* src, int32_t src_dtype, size_t rows
  * cfb200_select_kth_abs finds the k-th largest |v| under IEEE total order (NaN largest),
  * k = clamp(ceil((float)n * clamp(ratio, .001, .5)), 1, n) -- schemes.rs:522-530 -- and writes
  * it to thr_out[0] (device); k is returned through k_host.  workspace: device scratch of at
- * least cfb200_select_kth_workspace_bytes() bytes.
+ * least cfb200_select_kth_workspace_bytes() bytes (three histogram passes over the tensor).  With a 256-byte aligned
+ * workspace of cfb200_select_kth_workspace_bytes_for(n) bytes, a tensor of a million elements or more and a rank in the top
+ * 5 %, the tensor is read once instead: a sample brackets the threshold, one pass counts the keys above the bracket
+ * and collects those inside it, the exact rank is found among them; the bracket is verified on the device and the
+ * three passes run if it does not hold, so the answer is the exact k-th value either way.
  * cfb200_fakequant_group then applies, per flat group, scale = gmax<1e-12 ? 1 : gmax/qmax,
  * eff = (awq_salient && |v| >= thr) ? scale*0.5 : scale, out = clamp(round(v/eff))*eff. */
 size_t cfb200_select_kth_workspace_bytes(void);
+size_t cfb200_select_kth_workspace_bytes_for(size_t n);
 int32_t cfb200_select_kth_abs(const float* src, size_t n, float salient_ratio, float* thr_out,
                               uint64_t* k_host, void* workspace, size_t workspace_bytes,
                               void* stream);

@@ -278,6 +278,41 @@ def test_a2_select_kth(cuda_device, oracle, n, ratio):
     assert bits_equal(thr, np.array([want_thr], np.float32))
 
 
+@pytest.mark.parametrize("kind", ["gauss", "outliers", "ties", "two_values", "nan_inf", "sorted", "tiny_range"])
+@pytest.mark.parametrize("ratio", [0.001, 0.01, 0.05, 0.2])
+def test_a2_select_single_pass_path_is_exact(cuda_device, kind, ratio):
+    """Tensors large enough for the single-pass path (sample, bracket, one full pass, exact rank among the candidates;
+    ranks in the top 5 %) on distributions chosen to break a bracket: heavy ties, two distinct values, NaN / inf,
+    values sorted in memory, a range a sample cannot resolve.  The result must equal the k-th largest |v| under the
+    total order (torch.sort of the bit patterns) exactly, whichever path ran, and equal the three-pass path."""
+    from castforge_b200 import device as cf
+    n = (1 << 22) + 12345
+    g = torch.Generator(device=cuda_device).manual_seed(hash(kind) % 1000 + int(ratio * 1000))
+    w = torch.randn(n, device=cuda_device, generator=g) * 0.02
+    if kind == "outliers":
+        idx = torch.randint(0, n, (n // 500,), device=cuda_device, generator=g)
+        w[idx] *= 20
+    elif kind == "ties":
+        w = torch.round(w * 400) / 400                      # a few dozen distinct values
+    elif kind == "two_values":
+        w = torch.where(torch.rand(n, device=cuda_device, generator=g) < 0.03, torch.tensor(1.5, device=cuda_device), torch.tensor(-0.25, device=cuda_device))
+    elif kind == "nan_inf":
+        w[::1000] = float("nan")
+        w[5::3000] = float("inf")
+        w[7::3000] = float("-inf")
+    elif kind == "sorted":
+        w = torch.sort(w.abs()).values                      # the largest values all sit at the end of the buffer
+    elif kind == "tiny_range":
+        w = 1.0 + torch.rand(n, device=cuda_device, generator=g) * 1e-5   # every key shares its top 14 bits
+    thr, k = cf.select_kth_abs(w, ratio, single_pass=True)
+    thr3, k3 = cf.select_kth_abs(w, ratio, single_pass=False)
+    keys = (w.view(torch.int32) & 0x7FFFFFFF)
+    want = torch.sort(keys, descending=True).values[k - 1]
+    assert k == k3
+    assert int(thr.view(torch.int32).item()) == int(want.item()), (kind, ratio)
+    assert int(thr3.view(torch.int32).item()) == int(want.item()), (kind, ratio)
+
+
 @pytest.mark.parametrize("group", [2, 4, 32, 100, 128, 256])
 @pytest.mark.parametrize("awq", [True, False])
 def test_a2_groupwise(cuda_device, oracle, group, awq):
