@@ -21,7 +21,7 @@ import torch
 sys.path.insert(0, str(Path(__file__).resolve().parent))
 from castforge_b200 import device as D  # noqa: E402
 
-HBM_CASES = ("a1", "a1list", "a1layer", "gguf_q8_pack", "gguf_q8_unpack", "gguf_q4_unpack", "e1", "e2", "e3", "e4rows", "e4tensor", "a2", "a2awq", "a3", "a4", "a6", "fwht",
+HBM_CASES = ("a1", "a1list", "a1layer", "e4list", "gguf_q8_pack", "gguf_q8_unpack", "gguf_q4_unpack", "e1", "e2", "e3", "e4rows", "e4tensor", "a2", "a2awq", "a3", "a4", "a6", "fwht",
              "kv_page", "kv_head", "kv_tensor", "kv_decode", "e4m3_slice_enc", "e4m3_slice_dec",
              "merge_linear", "merge_slerp", "merge_ties", "task_merge", "prune_2to4", "prune_cols", "transpose", "lora_bake")
 GEMM_CASES = ("gemm_fp8", "gemm_bf16", "gemm_w4", "gemv_w4", "gptq")
@@ -86,6 +86,8 @@ def hbm_case(name, rows, cols, dt, rotate, dev):
         return codes, (lambda c: D.e4m3_slice_decode(c)), n * 5
     if name == "a1":
         return ws, (lambda w: D.quant_sym_tensor(w.reshape(-1), 8)), n * (esz + 1)
+    if name == "e4list":  # the per-tensor E4M3 cast of the whole rotation as ONE list call
+        return [ws], (lambda lst: D.cast_e4m3_tensors([w.reshape(-1) for w in lst])), rotate * n * (esz + 1)
     if name == "a1list":  # the whole rotation as ONE list call
         return [ws], (lambda lst: D.quant_sym_tensors([w.reshape(-1) for w in lst], 8)), rotate * n * (esz + 1)
     if name == "gguf_q8_pack":

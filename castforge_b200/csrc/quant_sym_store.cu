@@ -96,6 +96,25 @@ __device__ __forceinline__ void apply_vec(uint4 raw, size_t i, int8_t* __restric
   else st_stream4(codes + i * VE, packed[0]);
 }
 
+// One 16-byte vector -> VE E4M3FN codes: x = v * (1 / scale), round to nearest even, saturating at +-448, NaN -> 0x7F
+// (the arithmetic of cast_e4m3_tensor_kernel in quant_tensor.cu).
+template <int DT>
+__device__ __forceinline__ void apply_vec_e4m3(uint4 raw, size_t i, uint8_t* __restrict__ codes, float inv) {
+  constexpr int VE = Vec16<DT>::kElems;
+  float f[VE];
+  Vec16<DT>::unpack(raw, f);
+  auto pair = [&](float a, float b) -> uint32_t {  // a -> low byte
+    unsigned short pk;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pk) : "f"(__fmul_rn(b, inv)), "f"(__fmul_rn(a, inv)));
+    return pk;
+  };
+  uint32_t packed[VE / 4];
+#pragma unroll
+  for (int w = 0; w < VE / 4; ++w) packed[w] = pair(f[4 * w], f[4 * w + 1]) | (pair(f[4 * w + 2], f[4 * w + 3]) << 16);
+  if constexpr (VE == 8) st_stream8(codes + i * VE, make_uint2(packed[0], packed[1]));
+  else st_stream4(codes + i * VE, packed[0]);
+}
+
 template <int DT, bool TRUSTED>
 __device__ __forceinline__ void apply_part(const Seg& sg, float qmin, float qmax, bool demote) {
   constexpr int VE = Vec16<DT>::kElems;
@@ -540,7 +559,8 @@ __device__ __forceinline__ uint32_t items_of(const PGroup& grp, uint32_t bid, ui
 //   * then pass-2 reloads of group p (oldest chunk first: the lines L2 gives up first) alternate with
 //     the pass-1 items of group p+1 in proportion to their counts;
 //   * the last kPBufs pass-1 items of group p+1 close the phase and stay in the ring.
-template <int DT>
+// OUT: 0 = symmetric integer codes (A1), 1 = E4M3FN codes with scale = absmax / 448 (the per-tensor FP8 weight cast)
+template <int DT, int OUT = 0>
 __global__ void __launch_bounds__(kPThreads, 1)
 a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float qmin, float qmax, uint32_t retain_items,
                   uint32_t bar_sleep_ns, uint32_t tail_first) {
@@ -620,7 +640,21 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
     const float scale = grp.scale[it.seg], inv = grp.inv[it.seg];
     int8_t* codes = grp.codes[it.seg];
     const size_t v0 = (size_t)it.chunk * kPItemVecs;
-    if (it.vecs == (uint32_t)kPItemVecs && grp.odd[it.seg] == 0u) {
+    if constexpr (OUT == 1) {
+      uint8_t* c8 = reinterpret_cast<uint8_t*>(codes);
+      if (it.vecs == (uint32_t)kPItemVecs) {
+#pragma unroll
+        for (int h = 0; h < VPT; h += 4) {
+          uint4 r[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) r[u] = buf[tid + (h + u) * kPConsumers];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) apply_vec_e4m3<DT>(r[u], v0 + tid + (h + u) * kPConsumers, c8, inv);
+        }
+      } else {
+        for (uint32_t v = tid; v < it.vecs; v += kPConsumers) apply_vec_e4m3<DT>(buf[v], v0 + v, c8, inv);
+      }
+    } else if (it.vecs == (uint32_t)kPItemVecs && grp.odd[it.seg] == 0u) {
 #pragma unroll
       for (int h = 0; h < VPT; h += 4) {
         uint4 r[4];
@@ -705,7 +739,13 @@ a1_persist_kernel(const PSeg* __restrict__ segs, int count, unsigned* bar, float
           const float scale = cur.scale[s2];
           if (tid < (int)(cur.n[s2] - nv * VE)) {
             const size_t k = nv * VE + tid;
-            cur.codes[s2][k] = (int8_t)clamp_to_int(roundf(__fdiv_rn(load_elem<DT>(cur.src[s2], k), scale)), qmin, qmax);
+            if constexpr (OUT == 1) {
+              unsigned short pk;
+              asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(pk) : "f"(0.0f), "f"(__fmul_rn(load_elem<DT>(cur.src[s2], k), cur.inv[s2])));
+              cur.codes[s2][k] = (int8_t)(pk & 0xffu);
+            } else {
+              cur.codes[s2][k] = (int8_t)clamp_to_int(roundf(__fdiv_rn(load_elem<DT>(cur.src[s2], k), scale)), qmin, qmax);
+            }
           }
         }
       }
@@ -879,16 +919,16 @@ int plan_groups(int32_t count, const size_t* ns, int32_t dt, size_t budget, int*
   return ng;
 }
 
-template <int DT>
+template <int DT, int OUT>
 int32_t launch_persist_dt(const PSeg* table, int count, unsigned* bar, float qmin, float qmax, cudaStream_t st) {
   static int ready[64];
   int dev = 0;
   CFB_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) dev = 0;
   if (!ready[dev]) {
-    CFB_CUDA(cudaFuncSetAttribute(a1_persist_kernel<DT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmemBytes));
+    CFB_CUDA(cudaFuncSetAttribute(a1_persist_kernel<DT, OUT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmemBytes));
     int per_sm = 0;
-    CFB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, a1_persist_kernel<DT>, kPThreads, kPSmemBytes));
+    CFB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, a1_persist_kernel<DT, OUT>, kPThreads, kPSmemBytes));
     if (per_sm < 1) return set_error(CFB200_ERR_UNSUPPORTED, "the persistent A1 kernel does not fit this device");
     ready[dev] = 1;
   }
@@ -899,7 +939,7 @@ int32_t launch_persist_dt(const PSeg* table, int count, unsigned* bar, float qmi
   uint32_t tail_first = tunable(kTuneA1TailFirst) != 0;
   void* args[] = {(void*)&table, (void*)&count, (void*)&bar, (void*)&qmin, (void*)&qmax, (void*)&retain_items,
                   (void*)&bar_sleep_ns, (void*)&tail_first};
-  CFB_CUDA(cudaLaunchCooperativeKernel((const void*)a1_persist_kernel<DT>, dim3((unsigned)sm_count()), dim3(kPThreads), args,
+  CFB_CUDA(cudaLaunchCooperativeKernel((const void*)a1_persist_kernel<DT, OUT>, dim3((unsigned)sm_count()), dim3(kPThreads), args,
                                        (size_t)kPSmemBytes, st));
   return CFB200_OK;
 }
@@ -907,7 +947,7 @@ int32_t launch_persist_dt(const PSeg* table, int count, unsigned* bar, float qmi
 // The whole list through the persistent kernel, kPMaxTensors tensors per launch.
 int32_t run_persist(int32_t count, const void* const* srcs, int32_t dt, const size_t* ns, float qmin, float qmax,
                     int8_t* const* codes, float* scale_absmax, const int* group_end, int ng, size_t budget, void* const* stage_events,
-                    cudaStream_t st) {
+                    cudaStream_t st, int out_kind = 0) {
   // Descriptor tables and barrier words are handed out round-robin, per device.  A slot is reused only after the launch
   // that last read it has finished (an event per slot, waited for on the host), so any number of calls may be in
   // flight on any streams and host threads.
@@ -953,9 +993,9 @@ int32_t run_persist(int32_t count, const void* const* srcs, int32_t dt, const si
     int32_t rc;
     const int n = (int)host.size();
     switch (dt) {
-      case CFB200_F32: rc = launch_persist_dt<CFB200_F32>(table, n, bar, qmin, qmax, st); break;
-      case CFB200_F16: rc = launch_persist_dt<CFB200_F16>(table, n, bar, qmin, qmax, st); break;
-      default: rc = launch_persist_dt<CFB200_BF16>(table, n, bar, qmin, qmax, st); break;
+      case CFB200_F32: rc = out_kind ? launch_persist_dt<CFB200_F32, 1>(table, n, bar, qmin, qmax, st) : launch_persist_dt<CFB200_F32, 0>(table, n, bar, qmin, qmax, st); break;
+      case CFB200_F16: rc = out_kind ? launch_persist_dt<CFB200_F16, 1>(table, n, bar, qmin, qmax, st) : launch_persist_dt<CFB200_F16, 0>(table, n, bar, qmin, qmax, st); break;
+      default: rc = out_kind ? launch_persist_dt<CFB200_BF16, 1>(table, n, bar, qmin, qmax, st) : launch_persist_dt<CFB200_BF16, 0>(table, n, bar, qmin, qmax, st); break;
     }
     if (rc) return rc;
     CFB_CUDA(cudaEventRecord(slot_done[dev][slot], st));
@@ -1130,3 +1170,33 @@ extern "C" int32_t cfb200_quant_sym_tensors(int32_t count, const void* const* sr
   return rc;
 }
 
+
+// E4: the per-tensor E4M3FN weight cast over a whole list of tensors, through the same cooperative launch as A1 (absmax
+// pass of a group under the cast pass of the previous one, tails kept on chip): scale = absmax < 1e-12 ? 1 : absmax / 448,
+// codes = e4m3(v * (1 / scale)), identical to cfb200_cast_e4m3_tensor tensor by tensor.
+extern "C" int32_t cfb200_cast_e4m3_tensors(int32_t count, const void* const* srcs, int32_t src_dtype, const size_t* ns,
+                                            uint8_t* const* codes, float* scale_absmax, size_t l2_group_bytes, void* stream) {
+  CFB_CHECK_ARG(count >= 0, "negative count");
+  if (count == 0) return CFB200_OK;
+  CFB_CHECK_ARG(srcs && ns && codes && scale_absmax, "NULL argument");
+  CFB_CHECK_ARG(dtype_ok(src_dtype), "unknown src_dtype %d", src_dtype);
+  CFB_CHECK_ALIGNED(scale_absmax, 8);
+  for (int i = 0; i < count; ++i) {
+    CFB_CHECK_ARG(ns[i] == 0 || (srcs[i] && codes[i]), "tensor %d: NULL buffer", i);
+    CFB_CHECK_ALIGNED(srcs[i], 16);
+    CFB_CHECK_ALIGNED(codes[i], 16);
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone)
+    return set_error(CFB200_ERR_UNSUPPORTED, "cfb200_cast_e4m3_tensors copies a descriptor table from host memory: not under stream capture");
+  int* ge = new int[count];
+  const int ng = plan_groups(count, ns, src_dtype, l2_group_bytes, ge);
+  int32_t rc = CFB200_OK;
+  if (cudaMemsetAsync(scale_absmax, 0, (size_t)count * 2 * sizeof(float), st) != cudaSuccess) rc = set_error(CFB200_ERR_CUDA, "cudaMemsetAsync failed");
+  if (rc == CFB200_OK)
+    rc = run_persist(count, srcs, src_dtype, ns, -448.0f, 448.0f, reinterpret_cast<int8_t* const*>(codes), scale_absmax, ge, ng,
+                     l2_group_bytes ? l2_group_bytes : default_group_bytes(), nullptr, st, 1);
+  delete[] ge;
+  return rc;
+}

@@ -263,6 +263,24 @@ EPILOGUES = {None: 0, "none": 0, "bias": 1, "bias_relu": 2, "relu": 2, "bias_tan
              "silu": 4, "bias_gelu": 5, "gelu": 5, "bias_scale": 6}
 
 
+def cast_e4m3_tensors(ws: list[torch.Tensor], l2_group_bytes: int = 0):
+    """E4 per-tensor E4M3FN cast over a list of same-dtype device tensors in one cooperative launch.
+    Returns (codes list, scale_absmax f32[len, 2])."""
+    if not ws:
+        return [], None
+    ws = [_src(w) for w in ws]
+    dev, dt = ws[0].device, _dt(ws[0])
+    cnt = len(ws)
+    with torch.cuda.device(dev):
+        codes = [torch.empty(w.numel(), dtype=torch.uint8, device=dev) for w in ws]
+        sa = torch.empty((cnt, 2), dtype=torch.float32, device=dev)
+        srcs = (ctypes.c_void_p * cnt)(*[w.data_ptr() for w in ws])
+        outs = (ctypes.c_void_p * cnt)(*[c.data_ptr() for c in codes])
+        ns = (ctypes.c_size_t * cnt)(*[w.numel() for w in ws])
+        check(load().cfb200_cast_e4m3_tensors(cnt, srcs, dt, ns, outs, _p(sa), l2_group_bytes, _stream(ws[0])))
+    return codes, sa
+
+
 def _f32dev(t):
     assert t.is_cuda and t.dtype == torch.float32
     return t.contiguous()

@@ -232,6 +232,13 @@ int32_t cfb200_cast_e4m3_rows(const void* src, int32_t src_dtype, size_t rows, s
 int32_t cfb200_cast_e4m3_tensor(const void* src, int32_t src_dtype, size_t n, uint8_t* codes,
                                 float* scale_absmax, void* stream);
 
+/* The per-tensor cast over a whole list of device-resident tensors (the weights of a store on their way to the FP8
+ * GEMM) in one cooperative launch per 1024 tensors, with the schedule of cfb200_quant_sym_tensors: arguments as there,
+ * scale_absmax = {scale, absmax} per tensor; results identical to cfb200_cast_e4m3_tensor tensor by tensor.  Copies a
+ * descriptor table from host memory: not under stream capture.  cfb200_quant_sym_status reports its waits too. */
+int32_t cfb200_cast_e4m3_tensors(int32_t count, const void* const* srcs, int32_t src_dtype, const size_t* ns,
+                                 uint8_t* const* codes, float* scale_absmax, size_t l2_group_bytes, void* stream);
+
 /* ---- A8: interpreter dequantize + GEMM, bit-exact ----------------------------------------------
  * Replaces eval_matmul_2d (src/codegen/eval.rs:1465-1507) and the fused_qmatmul epilogues
  * (:1145-1179): C[m,n] = sum_k A[m,k]*B, products added in ascending k with separately rounded

@@ -520,6 +520,27 @@ def test_e3_workspace_too_small_is_rejected(cuda_device):
 
 
 # ------------------------------------------------------------------------------------------- E4
+@pytest.mark.parametrize("dtype", ["f32", "bf16", "f16"])
+def test_e4_tensor_list_equals_single_tensor_casts(cuda_device, dtype):
+    """cfb200_cast_e4m3_tensors (the cooperative list launch): codes and {scale, absmax} EQUAL cfb200_cast_e4m3_tensor
+    tensor by tensor -- ragged sizes, tails shorter than a vector, tensors larger than the on-chip ring, NaN / inf, zeros."""
+    from castforge_b200 import device as cf
+    sizes = [4096 * 1024 + 3, 7, 1, 33 * 1000, 12_000_017, 64, 2_000_000]
+    ws = [weights(n, n % 13 + 5, DT[dtype]).to(cuda_device) for n in sizes]
+    ws[3][17] = float("nan")
+    ws[6][5] = float("inf")
+    ws[5].zero_()
+    codes, sa = cf.cast_e4m3_tensors(ws)
+    import ctypes
+    import castforge_b200
+    for i, w in enumerate(ws):
+        c1, s1 = cf.cast_e4m3_tensor(w)
+        assert torch.equal(codes[i], c1), (dtype, i)
+        assert torch.equal(sa[i].view(torch.int32), s1.view(torch.int32)), (dtype, i)
+    flag = ctypes.c_int32(-1)
+    assert castforge_b200.load().cfb200_quant_sym_status(ctypes.byref(flag)) == 0 and flag.value == 0
+
+
 def test_e4_hardware_cast_matches_codec_on_covering_set(cuda_device, oracle):
     """Every code's exact value, each midpoint between adjacent codes, one ulp either side of it,
     values around the saturation point, zeros, NaN and infinities.  With the row absmax equal to
