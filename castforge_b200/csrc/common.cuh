@@ -30,6 +30,7 @@ enum Tunable {
   kTuneW4SplitK = 8,   // W4A16 prefill: 0 = automatic split-K for M <= 256, 1 = never, n > 1 = at most n slices
   kTuneA1BarSleep = 9, // persistent A1: nanoseconds between two polls of the grid barrier (0 = poll back to back)
   kTuneA1TailFirst = 10, // persistent A1: the quantize pass re-reads the lines kept in L2 before the ones that were let go
+  kTuneGemmPair = 11,  // tensor-core GEMMs: two CTAs (a cluster, two SMs) per 256 x 256 tile where the shape has one
   kTuneCount
 };
 long long tunable(int id);

@@ -414,7 +414,15 @@ __device__ __forceinline__ void trace_stamp(uint32_t bid, uint32_t G, int phase,
     g_ptrace[c][phase][slot] = t;
   }
 }
-#define CFB_TRACE(slot) trace_stamp(bid, G, p + 1, slot)
+static __device__ unsigned long long g_ptrace_all[160][32][2];  // every CTA: barrier arrival and barrier completion
+__device__ __forceinline__ void trace_all(uint32_t bid, int phase, int which) {
+  if (bid < 160 && phase >= 0 && phase < 32) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    g_ptrace_all[bid][phase][which] = t;
+  }
+}
+#define CFB_TRACE(slot) do { trace_stamp(bid, G, p + 1, slot); if ((slot) == 3) trace_all(bid, p + 1, 0); if ((slot) == 4) trace_all(bid, p + 1, 1); } while (0)
 #else
 #define CFB_TRACE(slot) do {} while (0)
 #endif
@@ -1024,6 +1032,11 @@ extern "C" int32_t cfb200_quant_sym_status(int32_t* flag_host) {
 extern "C" int32_t cfb200_debug_a1_trace(unsigned long long* host_out /* 3 * 200 * 8 */) {
   CFB_CUDA(cudaDeviceSynchronize());
   CFB_CUDA(cudaMemcpyFromSymbol(host_out, g_ptrace, sizeof(unsigned long long) * 3 * kTracePhases * kTraceSlots));
+  return CFB200_OK;
+}
+extern "C" int32_t cfb200_debug_a1_trace_all(unsigned long long* host_out /* 160 * 32 * 2 */) {
+  CFB_CUDA(cudaDeviceSynchronize());
+  CFB_CUDA(cudaMemcpyFromSymbol(host_out, g_ptrace_all, sizeof(unsigned long long) * 160 * 32 * 2));
   return CFB200_OK;
 }
 #endif

@@ -119,6 +119,82 @@ def test_w4a16_with_static_quantize_prologue(cuda_device, oracle, adt, shape):
     assert rel_err(got, unfused.double()) < 1e-2
 
 
+@pytest.fixture
+def pair_knob():
+    """Sets the "gemm_pair" knob (0 = one CTA per tile, 2 = the two-CTA kernel wherever it can run) and restores the default."""
+    from castforge_b200 import load
+    def set_knob(v):
+        assert load().cfb200_tune(b"gemm_pair", v) == 0
+    yield set_knob
+    set_knob(1)
+
+
+@pytest.mark.parametrize("shape", [(129, 100, 64), (256, 256, 64), (300, 700, 4096), (1000, 520, 264), (513, 1000, 4096), (2048, 4096, 1024)])
+def test_pair_kernel_bf16_and_fp8_match_the_one_cta_kernel(cuda_device, pair_knob, shape):
+    """The two-CTA (cta_group::2, 256 x 256 tile) kernel against the one-CTA kernel on the same operands: both sum the same
+    K slices in the same order, so the f32 results agree to the last bits; and against the f64 product."""
+    from castforge_b200 import device as cf
+    M, N, K = shape
+    g = torch.Generator(device=cuda_device).manual_seed(M * 5 + N + K)
+    a = torch.randn(M, K, device=cuda_device, generator=g).to(torch.bfloat16)
+    b = torch.randn(N, K, device=cuda_device, generator=g).to(torch.bfloat16)
+    pair_knob(0)
+    one = cf.gemm_bf16_nt(a, b, 0.75, True)
+    one_bf = cf.gemm_bf16_nt(a, b, 0.75, False)
+    pair_knob(2)
+    two = cf.gemm_bf16_nt(a, b, 0.75, True)
+    two_bf = cf.gemm_bf16_nt(a, b, 0.75, False)
+    assert rel_err(two, 0.75 * (a.double() @ b.double().T)) < 1e-4
+    assert rel_err(two, one) < 1e-6 and rel_err(two_bf.float(), one_bf.float()) < 1e-6
+    if K % 16 == 0:
+        ac, asc = cf.cast_e4m3_rows(a)
+        wc, wsa = cf.cast_e4m3_tensor((b.float() * 0.02).to(torch.bfloat16))
+        pair_knob(0)
+        f_one = cf.gemm_fp8(ac, asc, wc, float(wsa[0]), out_f32=True)
+        pair_knob(2)
+        f_two = cf.gemm_fp8(ac, asc, wc, float(wsa[0]), out_f32=True)
+        ref = (ac.view(torch.float8_e4m3fn).double() @ wc.view(torch.float8_e4m3fn).double().T) * asc.double()[:, None] * float(wsa[0])
+        assert rel_err(f_two, ref) < 1e-4 and rel_err(f_two, f_one) < 1e-6
+
+
+def test_pair_kernel_symmetric_upper_only(cuda_device, pair_knob):
+    """Upper-triangle-only product through the two-CTA kernel: tiles strictly below the diagonal stay untouched."""
+    from castforge_b200 import device as cf
+    g = torch.Generator(device=cuda_device).manual_seed(6)
+    xt = torch.randn(1280, 1024, device=cuda_device, generator=g).to(torch.bfloat16)
+    pair_knob(2)
+    h = cf.gemm_bf16_nt(xt, xt, 1.0, True, upper_only=True)
+    ref = xt.double() @ xt.double().T
+    iu = torch.triu_indices(1280, 1280, device=cuda_device)
+    assert float((h.double()[iu[0], iu[1]] - ref[iu[0], iu[1]]).abs().max() / ref.pow(2).mean().sqrt()) < 1e-3
+    assert float(h[768:, :256].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("shape", [(257, 256, 128), (300, 1000, 1024), (1024, 4096, 4096), (2048, 520, 14336)])
+def test_pair_kernel_w4a16_matches_the_one_cta_kernel(cuda_device, pair_knob, shape):
+    """W4A16 prefill through the two-CTA kernel (each CTA unpacks its 128 of the tile's 256 weight rows) against the one-CTA
+    kernel: the unpacked f16 weights are the same bits and the K order is the same."""
+    from castforge_b200 import device as cf
+    M, N, K = shape
+    g = torch.Generator(device=cuda_device).manual_seed(M + 11 * N)
+    w = torch.randn(N, K, device=cuda_device, generator=g) * 0.02
+    w.view(-1)[torch.randint(0, N * K, (max(1, N * K // 1000),), device=cuda_device, generator=g)] *= 20
+    a = torch.randn(M, K, device=cuda_device, generator=g).to(torch.bfloat16)
+    codes, scales, zps = cf.quant_int4_asym(w.reshape(-1), 128)
+    pair_knob(0)
+    one = cf.gemm_w4a16(a, codes, scales, zps, N, 128, out_f32=True)
+    pair_knob(2)
+    two = cf.gemm_w4a16(a, codes, scales, zps, N, 128, out_f32=True)
+    two_bf = cf.gemm_w4a16(a, codes, scales, zps, N, 128, out_f32=False)
+    ng = K // 128
+    q = torch.stack([codes & 0xF, codes >> 4], 1).reshape(N, ng, 128).double()
+    zz = torch.stack([zps & 0xF, zps >> 4], 1).reshape(-1)[: N * ng].reshape(N, ng, 1).double()
+    wd = ((q - zz) * scales.double().reshape(N, ng, 1)).reshape(N, K)
+    ref = a.double() @ wd.T
+    assert rel_err(two, ref) < 1e-2 and rel_err(two_bf.float(), ref) < 4e-2     # + bf16 output rounding (2^-9 of the largest value)
+    assert rel_err(two, one) < 1e-6
+
+
 @pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("NK", [(4096, 4096), (264, 1024), (14336, 4096), (40, 128), (4096, 14336), (8200, 4096), (76040, 4096)])
 def test_w4a16_decode(cuda_device, oracle, M, NK):
