@@ -654,19 +654,23 @@ __device__ __forceinline__ void store_row32(const GemmArgs& args, int row, int c
   if (args.out_f32) {
     float* dst = reinterpret_cast<float*>(args.C) + (size_t)row * args.ldc + col0;
     if (col0 + 32 <= args.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+      float4* d4 = reinterpret_cast<float4*>(dst);
+      float4 o[8];
+      if (args.accumulate) {  // all eight loads of the old values first: behind each other's stores they would run one memory latency at a time
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
+        for (int j = 0; j < 8; ++j) o[j] = __ldcg(d4 + j);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
         float4 v;
-        v.x = __uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f);
-        v.y = __uint_as_float(r[j + 1]) * rs * (args.col_scale ? args.col_scale[col0 + j + 1] : 1.0f);
-        v.z = __uint_as_float(r[j + 2]) * rs * (args.col_scale ? args.col_scale[col0 + j + 2] : 1.0f);
-        v.w = __uint_as_float(r[j + 3]) * rs * (args.col_scale ? args.col_scale[col0 + j + 3] : 1.0f);
-        float4* d4 = reinterpret_cast<float4*>(dst + j);
+        v.x = __uint_as_float(r[4 * j]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j] : 1.0f);
+        v.y = __uint_as_float(r[4 * j + 1]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j + 1] : 1.0f);
+        v.z = __uint_as_float(r[4 * j + 2]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j + 2] : 1.0f);
+        v.w = __uint_as_float(r[4 * j + 3]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j + 3] : 1.0f);
         if (args.accumulate) {
-          const float4 o = *d4;
-          v.x = __fadd_rn(o.x, v.x); v.y = __fadd_rn(o.y, v.y); v.z = __fadd_rn(o.z, v.z); v.w = __fadd_rn(o.w, v.w);
+          v.x = __fadd_rn(o[j].x, v.x); v.y = __fadd_rn(o[j].y, v.y); v.z = __fadd_rn(o[j].z, v.z); v.w = __fadd_rn(o[j].w, v.w);
         }
-        *d4 = v;
+        d4[j] = v;
       }
     } else {
 #pragma unroll
