@@ -55,7 +55,9 @@ const char* cfb200_version(void);
  * launch's grid barrier, default 0), "gemv_ring" (1, default: decode
  * shapes with 16 MB of packed weights or more use the shared-memory ring kernel; 0: never; n > 1: from n MB), "gemv_ring_rounds", "w4_split_k" (W4A16 prefill
  * with M <= 256: 0 = automatic split-K, 1 = never, n = at most n slices; changes the summation
- * order of the f32 accumulation and nothing else). */
+ * order of the f32 accumulation and nothing else), "gemm_pair" (the bf16 / FP8 / W4A16-prefill products: 1, default =
+ * two CTAs of a cluster (two SMs, tcgen05 cta_group::2) per 256 x 256 tile where the product has at least 56 such tiles
+ * (W4A16: M > 256 and 32 tiles); 0 = always one CTA per tile; 2 = pairs wherever M > 128 (W4A16: M > 256). */
 int32_t cfb200_tune(const char* key, int64_t value);
 
 /* ---- A1: per-tensor symmetric INT8 / INT4 ------------------------------------------------
