@@ -59,9 +59,11 @@ sgemm_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, long
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * kSgBM, n0 = blockIdx.x * kSgBN;
   // mode bit 0: only tiles that touch the lower triangle of C are wanted (symmetric update);
-  // mode bit 1: B is lower triangular (B(k, n) = 0 for k < n), so the k loop of a tile starts at its first column
+  // mode bit 1: B is lower triangular (B(k, n) = 0 for k < n), so the k loop of a tile starts at its first column;
+  // mode bit 2: A is lower triangular (A(m, k) = 0 for k > m), so the k loop of a tile ends with its last row
   if ((mode & 1) && n0 > m0 + kSgBM - 1) return;
   const int k_begin = (mode & 2) ? (n0 / kSgBK) * kSgBK : 0;
+  if (mode & 4) K = min(K, m0 + kSgBM);
   // element e of a tile (e = 0 .. 2047): (mm, kk) with the contiguous dimension fastest
   const bool a_m_fast = (rsA == 1), b_n_fast = (csB == 1);
   float ra[8], rb[8];
@@ -415,17 +417,31 @@ extern "C" int32_t cfb200_gptq_prepare(const float* H, size_t K, float damp_rati
   diag_mean_kernel<<<1, 256, 0, st>>>(H, n, mean);
   reverse_kernel<<<g16, b16, 0, st>>>(H, n, mean, damp_ratio, A, 0);
   fill_kernel<<<1024, 256, 0, st>>>(Xi, K * K, 0.0f);
-  const int nblk = (n + kNB - 1) / kNB;
-  for (int kb = 0; kb < nblk; ++kb) {
-    const int k0 = kb * kNB;
-    chol_diag_kernel<<<1, 256, 0, st>>>(A, n, k0, dinv);
-    copy_block_kernel<<<1, 256, 0, st>>>(dinv, Xi, n, k0);
-    const int r = n - k0 - kNB;
-    if (r > 0) {
+  // Blocked Cholesky on two levels.  Inside an outer panel of kOuter columns the 64-column steps update only the rest of
+  // the panel; what lies right of the panel gets ONE update per panel with all kOuter columns (a K = 512 product instead
+  // of eight K = 64 products: an eighth of the passes over the trailing matrix, and a multiply loop long enough to pay
+  // for a tile's loads and stores).
+  constexpr int kOuter = 8 * kNB;
+  for (int p0 = 0; p0 < n; p0 += kOuter) {
+    const int p1 = std::min(n, p0 + kOuter);
+    for (int k0 = p0; k0 < p1; k0 += kNB) {
+      chol_diag_kernel<<<1, 256, 0, st>>>(A, n, k0, dinv);
+      copy_block_kernel<<<1, 256, 0, st>>>(dinv, Xi, n, k0);
+      const int r = n - k0 - kNB;
+      if (r <= 0) continue;
       panel_trsm_kernel<<<(r + kNB - 1) / kNB, 256, 0, st>>>(A, n, k0, dinv);
-      const float* P = A + (size_t)(k0 + kNB) * n + k0;  // r x kNB panel
-      float* T = A + (size_t)(k0 + kNB) * n + k0 + kNB;   // trailing r x r
-      sgemm(st, r, r, kNB, -1.0f, P, n, 1, P, 1, n, 1.0f, T, n, 1);  // T -= P P^T, lower-triangle tiles only
+      const int c = p1 - k0 - kNB;  // columns of the panel right of this step
+      if (c > 0) {
+        const float* P = A + (size_t)(k0 + kNB) * n + k0;  // r x kNB
+        float* T = A + (size_t)(k0 + kNB) * n + k0 + kNB;   // r x c, lower-triangle tiles only
+        sgemm(st, r, c, kNB, -1.0f, P, n, 1, P, 1, n, 1.0f, T, n, 1);
+      }
+    }
+    const int r2 = n - p1;
+    if (r2 > 0) {
+      const float* P = A + (size_t)p1 * n + p0;  // r2 x (p1 - p0)
+      float* T = A + (size_t)p1 * n + p1;        // trailing r2 x r2
+      sgemm(st, r2, r2, p1 - p0, -1.0f, P, n, 1, P, 1, n, 1.0f, T, n, 1);
     }
   }
   // L^-1 by doubling: the diagonal 64-blocks are inverted already; at block size s every pair of neighbouring
@@ -436,12 +452,12 @@ extern "C" int32_t cfb200_gptq_prepare(const float* H, size_t K, float damp_rati
     float* tmp = U;                               // U is free until the end; T of a pair sits where its X21 goes
     const long o21 = (long)sz * n;                // offset of block (2,1) from a pair's origin; (2,2) is at o21 + sz
     sgemm(st, sz, sz, sz, 1.0f, A + o21, n, 1, Xi, n, 1, 0.0f, tmp + o21, n, 2, pairs, step, step, step);          // T = L21 * X11
-    sgemm(st, sz, sz, sz, -1.0f, Xi + o21 + sz, n, 1, tmp + o21, n, 1, 0.0f, Xi + o21, n, 0, pairs, step, step, step);  // X21 = -X22 * T
+    sgemm(st, sz, sz, sz, -1.0f, Xi + o21 + sz, n, 1, tmp + o21, n, 1, 0.0f, Xi + o21, n, 4, pairs, step, step, step);  // X21 = -X22 * T
     if (rem > sz) {  // a last pair whose second block is short
       const int sb = rem - sz;
       const long o = (long)pairs * step;
       sgemm(st, sb, sz, sz, 1.0f, A + o + o21, n, 1, Xi + o, n, 1, 0.0f, tmp + o + o21, n, 2);
-      sgemm(st, sb, sz, sb, -1.0f, Xi + o + o21 + sz, n, 1, tmp + o + o21, n, 1, 0.0f, Xi + o + o21, n, 0);
+      sgemm(st, sb, sz, sb, -1.0f, Xi + o + o21 + sz, n, 1, tmp + o + o21, n, 1, 0.0f, Xi + o + o21, n, 4);
     }
   }
   reverse_kernel<<<g16, b16, 0, st>>>(Xi, n, nullptr, 0.0f, U, 1);  // U = P L^-1 P (upper)
