@@ -48,7 +48,7 @@ struct GemmArgs {
   void* C;                  // [M, ldc] bf16 or f32
   int ldc;
   int out_f32;
-  int upper_only;           // skip tiles strictly below the diagonal (symmetric products)
+  int upper_only;           // 1: skip tiles strictly below the diagonal (symmetric products); 2: strictly above it
   int accumulate;           // f32 output only: C += result instead of C = result
   int* error_flag;          // device int, set non-zero when a bounded wait ran out
   int split_k;              // > 1: a tile's k-blocks are dealt to split_k CTAs, raw f32 partial sums go to `partial`
@@ -262,7 +262,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     kb_hi = min(num_kb, kb_lo + kb_per);
     m0 = (tt / tiles_n) * (AM * kBM);
     n0 = (tt % tiles_n) * BN;
-    return !(args.upper_only && (n0 + BN <= m0));  // (upper_only is used with AM == 1 only)
+    // triangle 1: a tile entirely below the diagonal is skipped; 2: a tile entirely above it (AM == 1 only)
+    return !((args.upper_only == 1 && n0 + BN <= m0) || (args.upper_only == 2 && m0 + AM * kBM <= n0));
   };
 
   if (threadIdx.x == 0) {
@@ -743,7 +744,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int rows = min(kBand, tiles_m - band * kBand);  // the last band may be shorter
     m0 = (band * kBand + r % rows) * (2 * kBM);
     n0 = (r / rows) * kPairBN;
-    return !(args.upper_only && (n0 + kPairBN <= m0));
+    return !((args.upper_only == 1 && n0 + kPairBN <= m0) || (args.upper_only == 2 && m0 + 2 * kBM <= n0));
   };
 
   if (threadIdx.x == 0) {
@@ -1173,14 +1174,18 @@ extern "C" int32_t cfb200_gemm_fp8(const uint8_t* A, const float* a_scales, cons
 
 // The bf16 product with explicit row pitches (lda, ldb in elements: the operands may be column ranges of wider
 // matrices) and an optional C += (f32 output only).
-extern "C" int32_t cfb200_gemm_bf16_nt_ld(const void* A, size_t lda, const void* B, size_t ldb, size_t M, size_t N, size_t K,
-                                          float alpha, void* C, int32_t out_f32, int32_t upper_only, int32_t accumulate,
+// The bf16 product with explicit row pitches (lda, ldb, ldc in elements: the operands and the result may be blocks of
+// wider matrices), a triangle selector (0 = all tiles, 1 = only tiles that touch the upper triangle, 2 = the lower) and an
+// optional C += (f32 output only).
+extern "C" int32_t cfb200_gemm_bf16_nt_ex(const void* A, size_t lda, const void* B, size_t ldb, size_t M, size_t N, size_t K,
+                                          float alpha, void* C, size_t ldc, int32_t out_f32, int32_t triangle, int32_t accumulate,
                                           int32_t* error_flag, void* stream) {
   CFB_CHECK_ARG(A && B && C, "NULL buffer");
   CFB_CHECK_ARG(M > 0 && N > 0 && K > 0 && K % 8 == 0, "bf16 GEMM needs K a positive multiple of 8 (got %zu)", K);
-  CFB_CHECK_ARG(M < (1u << 31) && N < (1u << 31) && K < (1u << 31), "dimension too large");
-  CFB_CHECK_ARG(lda >= K && ldb >= K, "row pitch shorter than K");
+  CFB_CHECK_ARG(M < (1u << 31) && N < (1u << 31) && K < (1u << 31) && ldc < (1u << 31), "dimension too large");
+  CFB_CHECK_ARG(lda >= K && ldb >= K && ldc >= N, "row pitch shorter than the row");
   CFB_CHECK_ARG(!accumulate || out_f32, "accumulation needs an f32 output");
+  CFB_CHECK_ARG(triangle >= 0 && triangle <= 2, "triangle is 0, 1 or 2");
   CUtensorMap tmA, tmB;
   int32_t rc = make_tmap(&tmA, A, 2, M, K, lda, kBM);
   if (rc) return rc;
@@ -1188,10 +1193,16 @@ extern "C" int32_t cfb200_gemm_bf16_nt_ld(const void* A, size_t lda, const void*
   if (rc) return rc;
   GemmArgs g = {};
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
-  g.alpha = alpha; g.C = C; g.ldc = (int)N; g.out_f32 = out_f32; g.upper_only = upper_only; g.accumulate = accumulate;
+  g.alpha = alpha; g.C = C; g.ldc = (int)ldc; g.out_f32 = out_f32; g.upper_only = triangle; g.accumulate = accumulate;
   g.error_flag = error_flag;
   if (use_pair_kernel(M, N, 56)) return launch_gemm_pair<kKindBF16, kBTma, 7>(tmA, tmB, g, (cudaStream_t)stream);
   return launch_gemm<128, kKindBF16, kBTma, 6>(tmA, tmB, g, (cudaStream_t)stream);
+}
+
+extern "C" int32_t cfb200_gemm_bf16_nt_ld(const void* A, size_t lda, const void* B, size_t ldb, size_t M, size_t N, size_t K,
+                                          float alpha, void* C, int32_t out_f32, int32_t upper_only, int32_t accumulate,
+                                          int32_t* error_flag, void* stream) {
+  return cfb200_gemm_bf16_nt_ex(A, lda, B, ldb, M, N, K, alpha, C, N, out_f32, upper_only ? 1 : 0, accumulate, error_flag, stream);
 }
 
 extern "C" int32_t cfb200_gemm_bf16_nt(const void* A, const void* B, size_t M, size_t N, size_t K, float alpha, void* C,

@@ -10,8 +10,11 @@
 //      row's CURRENT values at the block start), and pushes the error e = (w - q) / U[j,j] into the
 //      columns to its right: w[l] -= e * U[j,l].  The block's errors are then applied to all
 //      later columns with one GEMM (W[:, end:] -= E * U[block, end:]).
-// Everything after the Hessian is f32 on CUDA cores (the factorisation needs the precision and is
-// ~K^3 flops against the Hessian's 2*T*K^2).
+// The factorisation needs f32 precision (~K^3 flops against the Hessian's 2*T*K^2).  Its 64-column steps and small
+// products run as f32 on the CUDA cores; the large products (the trailing update of a 512-column panel, the upper levels
+// of the triangular inverse) run on the bf16 tensor cores with every f32 operand split into three bf16 numbers (see
+// split3).  The column walk and its error propagation are f32 on the CUDA cores in a fixed operation order, which the
+// CPU oracle repeats bit for bit.
 #include <math.h>
 
 #include "common.cuh"
@@ -19,6 +22,9 @@
 namespace cfb {
 namespace {
 
+#ifndef CFB_GPTQ_SPLITK
+#define CFB_GPTQ_SPLITK 1024
+#endif
 constexpr int kNB = 64;  // factorisation block
 
 // ---- bf16 transpose [R, C] -> [C, R] ------------------------------------------------------------
@@ -257,6 +263,64 @@ __global__ void copy_block_kernel(const float* __restrict__ dinv, float* __restr
   }
 }
 
+// ---- f32 products on the bf16 tensor cores ---------------------------------------------------------
+// x = h + m + l with h = bf16(x), m = bf16(x - h), l = bf16(x - h - m): 24 significant bits in three bf16 numbers.  A
+// product a * b is summed as  (h l + l h + m m) + (h m + m h) + h h,  six bf16 x bf16 products that are exact in the
+// tensor core's f32 accumulator; what is left out (m l, l m, l l) is below 2^-24 of a * b.  The six terms of a K-slice
+// become six K-blocks of ONE bf16 GEMM, smallest terms first, so that the accumulator's truncating additions act on the
+// small partial sums while they are alone and on h h only for the slice's own length (kSplitK / 16 additions); slices are
+// summed by the GEMM epilogue's rounded C +=.  Measured on damped Hessians of condition number ~850 (K = 4096) and at
+// K = 14336: || U^T U (H + damp) v - v || / || v || = 5e-7 and 2e-6 in f64 (3e-7 and 1e-6 with 512-column slices).
+constexpr int kSplitK = CFB_GPTQ_SPLITK;  // f32 columns per slice
+constexpr int kSplitW = 6 * kSplitK;      // bf16 columns of a slice's operand
+constexpr int kTcMin = 1024;              // products with fewer rows and columns than this stay on the CUDA cores
+
+__device__ __forceinline__ void split3(float x, __nv_bfloat16& h, __nv_bfloat16& m, __nv_bfloat16& l) {
+  h = __float2bfloat16_rn(x);
+  const float r1 = x - __bfloat162float(h);  // exact
+  m = __float2bfloat16_rn(r1);
+  l = __float2bfloat16_rn(r1 - __bfloat162float(m));
+}
+// block order along the bf16 K axis: left operand  h l m | h m | h,  right operand  l h m | m h | h
+__device__ __forceinline__ void put_left(__nv_bfloat16* row, int k, int kc, __nv_bfloat16 h, __nv_bfloat16 m, __nv_bfloat16 l) {
+  row[k] = h; row[kc + k] = l; row[2 * kc + k] = m; row[3 * kc + k] = h; row[4 * kc + k] = m; row[5 * kc + k] = h;
+}
+__device__ __forceinline__ void put_right(__nv_bfloat16* row, int k, int kc, __nv_bfloat16 h, __nv_bfloat16 m, __nv_bfloat16 l) {
+  row[k] = l; row[kc + k] = h; row[2 * kc + k] = m; row[3 * kc + k] = m; row[4 * kc + k] = h; row[5 * kc + k] = h;
+}
+// src [R, kc] f32 (row pitch ld) -> left and / or right operand [R, 6 * kc] bf16 (row pitch 6 * kSplitK; kc <= kSplitK,
+// the columns kc .. of a block that a short last slice leaves are never read: the GEMM's K is 6 * kc with blocks kc apart)
+__global__ void split_rows_kernel(const float* __restrict__ src, long ld, int R, int kc, __nv_bfloat16* __restrict__ left,
+                                  __nv_bfloat16* __restrict__ right) {
+  const long total = (long)R * kc;
+  for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / kc), k = (int)(i - (long)r * kc);
+    __nv_bfloat16 h, m, l;
+    split3(src[(long)r * ld + k], h, m, l);
+    if (left) put_left(left + (long)r * (6 * kc), k, kc, h, m, l);
+    if (right) put_right(right + (long)r * (6 * kc), k, kc, h, m, l);
+  }
+}
+// src [kc, R] f32 (row pitch ld: the operand's K runs down the rows) -> right operand [R, 6 * kc] bf16, through a
+// 32 x 32 shared-memory tile so that both sides are accessed along their rows
+__global__ void split_cols_kernel(const float* __restrict__ src, long ld, int R, int kc, __nv_bfloat16* __restrict__ right) {
+  __shared__ float tile[32][33];
+  const int r0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int k = k0 + j, r = r0 + threadIdx.x;
+    tile[j][threadIdx.x] = (k < kc && r < R) ? src[(long)k * ld + r] : 0.0f;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int r = r0 + j, k = k0 + threadIdx.x;
+    if (r < R && k < kc) {
+      __nv_bfloat16 h, m, l;
+      split3(tile[threadIdx.x][j], h, m, l);
+      put_right(right + (long)r * (6 * kc), k, kc, h, m, l);
+    }
+  }
+}
+
 // ---- the column walk ---------------------------------------------------------------------------------
 // truncating f32 -> f16 of the reference (tensor_store.rs:85-101), 0/inf/NaN -> 1.0 (as in the INT4 kernel)
 __device__ __forceinline__ unsigned f16_trunc_scale_bits(float v) {
@@ -358,6 +422,46 @@ extern "C" int32_t cfb200_gemm_bf16_nt_ld(const void* A, size_t lda, const void*
                                           float alpha, void* C, int32_t out_f32, int32_t upper_only, int32_t accumulate,
                                           int32_t* error_flag, void* stream);
 
+extern "C" int32_t cfb200_gemm_bf16_nt_ex(const void* A, size_t lda, const void* B, size_t ldb, size_t M, size_t N, size_t K,
+                                          float alpha, void* C, size_t ldc, int32_t out_f32, int32_t triangle, int32_t accumulate,
+                                          int32_t* error_flag, void* stream);
+
+namespace cfb {
+namespace {
+// C[M, N] (pitch ldc) += alpha * A[M, K] * B on the tensor cores, f32 operands split three ways (see split3).  B is given
+// by rows ([N, K], pitch ldb: b_rows) or by columns ([K, N], pitch ldb: b_cols); b_rows == A means a symmetric update
+// (both operands from one split pass).  a_lower: A is lower triangular, so slice k0 only has rows >= k0; b_lower: B (by
+// columns) is lower triangular, so slice k0 only reaches columns < k0 + slice.  wl / wr: [max(M, N), kSplitW] bf16 each.
+int32_t tc_product(cudaStream_t st, int M, int N, int K, float alpha, const float* A, long lda, const float* b_rows,
+                   const float* b_cols, long ldb, float* C, long ldc, int triangle, bool a_lower, bool b_lower,
+                   __nv_bfloat16* wl, __nv_bfloat16* wr, int32_t* flag) {
+  for (int k0 = 0; k0 < K; k0 += kSplitK) {
+    const int kc = std::min(kSplitK, K - k0);
+    const int m_lo = a_lower ? k0 : 0, m_eff = M - m_lo;
+    const int n_eff = b_lower ? std::min(N, k0 + kc) : N;
+    if (m_eff <= 0 || n_eff <= 0) continue;
+    const bool same = (b_rows == A) && !b_cols;
+    auto blocks = [](long total) { return (unsigned)std::min<long>((total + 255) / 256, (long)sm_count() * 16); };
+    split_rows_kernel<<<blocks((long)m_eff * kc), 256, 0, st>>>(A + (long)m_lo * lda + k0, lda, m_eff, kc, wl, same ? wr : nullptr);
+    if (b_cols) {
+      split_cols_kernel<<<dim3((unsigned)((n_eff + 31) / 32), (unsigned)((kc + 31) / 32)), dim3(32, 8), 0, st>>>(b_cols + (long)k0 * ldb, ldb, n_eff, kc, wr);
+    } else if (!same) {
+      split_rows_kernel<<<blocks((long)n_eff * kc), 256, 0, st>>>(b_rows + k0, ldb, n_eff, kc, nullptr, wr);
+    }
+    CFB_LAUNCH_CHECK();
+    const int32_t rc = cfb200_gemm_bf16_nt_ex(wl, (size_t)6 * kc, wr, (size_t)6 * kc, (size_t)m_eff, (size_t)n_eff, (size_t)6 * kc, alpha,
+                                              C + (long)m_lo * ldc, (size_t)ldc, 1, triangle, 1, flag, st);
+    if (rc) return rc;
+  }
+  return CFB200_OK;
+}
+// a bounded wait of a tensor-core launch that ran out makes the factor unusable: say so in the result itself
+__global__ void poison_if_flag_kernel(const int32_t* flag, float* U) {
+  if (*flag != 0) U[0] = __int_as_float(0x7fc00000);
+}
+}  // namespace
+}  // namespace cfb
+
 // H (K x K f32) = X^T X / T for X [T, K] bf16.  xt_workspace: T*K bf16 (the transposed copy).
 extern "C" size_t cfb200_gptq_hessian_workspace_bytes(size_t T, size_t K) { return T * K * 2; }
 
@@ -400,7 +504,10 @@ extern "C" int32_t cfb200_gptq_hessian_scaled(const void* X, size_t T, size_t K,
 }
 
 // U = upper Cholesky factor of (H + damp * mean(diag H) * I)^-1.  workspace: 2*K*K + 64*64 + 4 floats.
-extern "C" size_t cfb200_gptq_prepare_workspace_bytes(size_t K) { return (2 * K * K + kNB * kNB + 4) * sizeof(float); }
+extern "C" size_t cfb200_gptq_prepare_workspace_bytes(size_t K) {
+  // reversed matrix / factor, its inverse, a diagonal block, four words (mean, give-up flag), two split operands
+  return (2 * K * K + kNB * kNB + 4) * sizeof(float) + 2 * K * (size_t)kSplitW * sizeof(__nv_bfloat16);
+}
 
 extern "C" int32_t cfb200_gptq_prepare(const float* H, size_t K, float damp_ratio, float* U, void* workspace, size_t workspace_bytes,
                                        void* stream) {
@@ -413,6 +520,10 @@ extern "C" int32_t cfb200_gptq_prepare(const float* H, size_t K, float damp_rati
   float* Xi = A + K * K;                           // inverse of that factor
   float* dinv = Xi + K * K;
   float* mean = dinv + kNB * kNB;
+  int32_t* flag = reinterpret_cast<int32_t*>(mean + 2);
+  __nv_bfloat16* wl = reinterpret_cast<__nv_bfloat16*>(mean + 4);  // 16-byte aligned: every part before it is a multiple of 16 bytes
+  __nv_bfloat16* wr = wl + K * (size_t)kSplitW;
+  CFB_CUDA(cudaMemsetAsync(flag, 0, sizeof(int32_t), st));
   dim3 g16((unsigned)((K + 15) / 16), (unsigned)((K + 15) / 16)), b16(16, 16);
   diag_mean_kernel<<<1, 256, 0, st>>>(H, n, mean);
   reverse_kernel<<<g16, b16, 0, st>>>(H, n, mean, damp_ratio, A, 0);
@@ -441,7 +552,12 @@ extern "C" int32_t cfb200_gptq_prepare(const float* H, size_t K, float damp_rati
     if (r2 > 0) {
       const float* P = A + (size_t)p1 * n + p0;  // r2 x (p1 - p0)
       float* T = A + (size_t)p1 * n + p1;        // trailing r2 x r2
-      sgemm(st, r2, r2, p1 - p0, -1.0f, P, n, 1, P, 1, n, 1.0f, T, n, 1);
+      if (r2 >= kTcMin) {
+        const int32_t rc = tc_product(st, r2, r2, p1 - p0, -1.0f, P, n, P, nullptr, n, T, n, 2, false, false, wl, wr, flag);
+        if (rc) return rc;
+      } else {
+        sgemm(st, r2, r2, p1 - p0, -1.0f, P, n, 1, P, 1, n, 1.0f, T, n, 1);
+      }
     }
   }
   // L^-1 by doubling: the diagonal 64-blocks are inverted already; at block size s every pair of neighbouring
@@ -451,6 +567,19 @@ extern "C" int32_t cfb200_gptq_prepare(const float* H, size_t K, float damp_rati
     const long step = (long)2 * sz * n + 2 * sz;  // from one pair's blocks to the next pair's
     float* tmp = U;                               // U is free until the end; T of a pair sits where its X21 goes
     const long o21 = (long)sz * n;                // offset of block (2,1) from a pair's origin; (2,2) is at o21 + sz
+    if (sz >= kTcMin) {  // large blocks: both products on the tensor cores, pair by pair
+      for (int pi = 0; pi <= pairs; ++pi) {
+        const int sb = pi < pairs ? sz : rem - sz;  // rows of the pair's second block (the last pair may be short)
+        if (sb <= 0) break;
+        const long o = (long)pi * step;
+        CFB_CUDA(cudaMemset2DAsync(tmp + o + o21, (size_t)n * sizeof(float), 0, (size_t)sz * sizeof(float), (size_t)sb, st));
+        int32_t rc = tc_product(st, sb, sz, sz, 1.0f, A + o + o21, n, nullptr, Xi + o, n, tmp + o + o21, n, 0, false, true, wl, wr, flag);  // T = L21 * X11
+        if (rc) return rc;
+        rc = tc_product(st, sb, sz, sb, -1.0f, Xi + o + o21 + sz, n, nullptr, tmp + o + o21, n, Xi + o + o21, n, 0, true, false, wl, wr, flag);  // X21 = -X22 * T
+        if (rc) return rc;
+      }
+      continue;
+    }
     sgemm(st, sz, sz, sz, 1.0f, A + o21, n, 1, Xi, n, 1, 0.0f, tmp + o21, n, 2, pairs, step, step, step);          // T = L21 * X11
     sgemm(st, sz, sz, sz, -1.0f, Xi + o21 + sz, n, 1, tmp + o21, n, 1, 0.0f, Xi + o21, n, 4, pairs, step, step, step);  // X21 = -X22 * T
     if (rem > sz) {  // a last pair whose second block is short
@@ -461,6 +590,7 @@ extern "C" int32_t cfb200_gptq_prepare(const float* H, size_t K, float damp_rati
     }
   }
   reverse_kernel<<<g16, b16, 0, st>>>(Xi, n, nullptr, 0.0f, U, 1);  // U = P L^-1 P (upper)
+  poison_if_flag_kernel<<<1, 1, 0, st>>>(flag, U);
   CFB_LAUNCH_CHECK();
   return CFB200_OK;
 }

@@ -293,6 +293,11 @@ int32_t cfb200_gemm_bf16_nt(const void* A, const void* B, size_t M, size_t N, si
 int32_t cfb200_gemm_bf16_nt_ld(const void* A, size_t lda, const void* B, size_t ldb, size_t M, size_t N, size_t K,
                                float alpha, void* C, int32_t out_f32, int32_t upper_only, int32_t accumulate,
                                int32_t* error_flag, void* stream);
+/* The same product with a row pitch for C as well (ldc elements: C may be a block of a wider matrix) and a triangle
+ * selector: 0 = every tile, 1 = only the tiles that touch the upper triangle, 2 = only those that touch the lower. */
+int32_t cfb200_gemm_bf16_nt_ex(const void* A, size_t lda, const void* B, size_t ldb, size_t M, size_t N, size_t K,
+                               float alpha, void* C, size_t ldc, int32_t out_f32, int32_t triangle, int32_t accumulate,
+                               int32_t* error_flag, void* stream);
 size_t cfb200_gemm_w4a16_workspace_bytes(size_t M, size_t N, size_t K);
 int32_t cfb200_gemm_w4a16(const void* A, const uint8_t* w_codes, const uint16_t* w_scales,
                           const uint8_t* w_zps, size_t M, size_t N, size_t K, size_t group, void* C,
@@ -326,7 +331,10 @@ int32_t cfb200_gemv_w4a16_status(int32_t* flag_host);
  *                        (T % 8 == 0), on the tensor cores through cfb200_gemm_bf16_nt.
  *  cfb200_gptq_prepare:  U[K,K] f32 = the upper Cholesky factor of
  *                        (H + damp_ratio * mean(diag H) * I)^-1; a zero diagonal entry (dead input
- *                        channel) is replaced by 1.
+ *                        channel) is replaced by 1.  Products of 1024 rows and more inside the
+ *                        factorisation run on the bf16 tensor cores with f32 operands split three
+ *                        ways (f32-level accuracy); if a bounded wait of such a launch runs out,
+ *                        U[0] is set to NaN, so a factor with a positive diagonal is a good one.
  *  cfb200_gptq_quantize: W [N,K] (dtype code) -> codes / scales / zero_points in the layout of
  *                        cfb200_quant_int4_asym with group 128 along K, each column's rounding
  *                        error pushed into the columns right of it through U.  Rows are
