@@ -422,6 +422,25 @@ def gemm_bf16_nt(a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, out_f32: 
     return c
 
 
+def gemm_bf16_nt_into(c: torch.Tensor, a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0, triangle: int = 0, accumulate: bool = False):
+    """c (f32, row-major, possibly a block of a wider matrix: any row stride) = or += alpha * a @ b^T for bf16 a [M,K], b [N,K]
+    whose rows may be strided too (cfb200_gemm_bf16_nt_ex).  triangle: 0 all tiles, 1 / 2 only tiles touching the upper /
+    lower triangle.  Returns c."""
+    assert c.is_cuda and c.dtype == torch.float32 and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert c.stride(1) == 1 and a.stride(1) == 1 and b.stride(1) == 1
+    M, K = a.shape
+    N = b.shape[0]
+    assert c.shape == (M, N) and b.shape[1] == K
+    with torch.cuda.device(c.device):
+        flag = torch.zeros(1, dtype=torch.int32, device=c.device)
+        from ._lib import check as _chk
+        _chk(load().cfb200_gemm_bf16_nt_ex(_p(a), a.stride(0), _p(b), b.stride(0), M, N, K, float(alpha), _p(c), c.stride(0), 1, int(triangle),
+                                           int(bool(accumulate)), _p(flag), _stream(c)))
+        if int(flag.item()) != 0:
+            raise RuntimeError("gemm_bf16_nt_into: a bounded wait ran out inside the kernel")
+    return c
+
+
 def gemm_w4a16(a: torch.Tensor, codes: torch.Tensor, scales: torch.Tensor, zps: torch.Tensor, N: int, group: int = 128,
                out_f32: bool = False, check: bool = True):
     """C[M,N] = A_bf16 @ dequant(W)^T with W [N,K] in the packed INT4 layout of quant_int4_asym."""

@@ -204,6 +204,24 @@ def test_gptq_config5_sizes(oracle, cuda_device, N, K):
 
 
 @pytest.mark.gpu
+def test_gptq_factor_with_tensor_core_products_against_f64(cuda_device):
+    """K = 2048 is the smallest size at which the factorisation's large products (trailing update of a 512-column panel,
+    inverse level 1024) run on the bf16 tensor cores with three-way split operands: U against numpy's f64 factor."""
+    import torch
+    from castforge_b200 import device as D
+    K, T = 2048, 8192
+    W, X = make_case(77, 8, K, T)
+    xd = torch.from_numpy(bf16_round(X)).to(cuda_device, torch.bfloat16)
+    H = D.gptq_hessian(xd)
+    U = D.gptq_prepare(H, 0.01).cpu().numpy()
+    Hd = H.cpu().numpy().astype(np.float64)
+    Hd[np.diag_indices(K)] += 0.01 * float(np.mean(np.diag(Hd)))
+    Uref = np.linalg.cholesky(np.linalg.inv(Hd)).T
+    assert np.all(np.diag(U) > 0) and float(np.abs(np.tril(U, -1)).max()) == 0.0
+    assert np.abs(U - Uref).max() <= 1e-4 * np.abs(Uref).max()
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("N,K,T", [(64, 256, 1024), (200, 512, 2048), (8, 128, 256)])
 def test_gptq_cuda_vs_oracle(oracle, cuda_device, N, K, T):
     import torch

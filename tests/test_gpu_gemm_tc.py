@@ -170,6 +170,32 @@ def test_pair_kernel_symmetric_upper_only(cuda_device, pair_knob):
     assert float(h[768:, :256].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("knob", [0, 2])
+def test_bf16_product_into_a_block_with_triangle_and_accumulate(cuda_device, pair_knob, knob):
+    """cfb200_gemm_bf16_nt_ex: operands and result are blocks of wider matrices (row pitches), C -= A B^T on the tiles that
+    touch the lower triangle only, through both kernels."""
+    from castforge_b200 import device as cf
+    g = torch.Generator(device=cuda_device).manual_seed(9 + knob)
+    big = torch.randn(1600, 2000, device=cuda_device, generator=g)
+    wide = torch.randn(1300, 1024, device=cuda_device, generator=g).to(torch.bfloat16)
+    a = wide[:, 256:256 + 512]                       # [1300, 512], row pitch 1024
+    c = big[128:128 + 1300, 512:512 + 1300]          # [1300, 1300] block, row pitch 2000
+    before = c.clone()
+    pair_knob(knob)
+    cf.gemm_bf16_nt_into(c, a, a, alpha=-1.0, triangle=2, accumulate=True)
+    want = before.double() - a.double() @ a.double().T
+    low = torch.tril(torch.ones(1300, 1300, device=cuda_device, dtype=torch.bool))
+    assert float((c.double() - want)[low].abs().max()) < 1e-3          # f32 accumulation of 512 products of N(0,1) values
+    tile = 256 if knob else 128
+    far = torch.triu(torch.ones(1300, 1300, device=cuda_device, dtype=torch.bool), diagonal=2 * tile)   # surely in a skipped tile
+    assert torch.equal(c[far], before[far])
+    outside = big.clone()
+    outside[128:128 + 1300, 512:512 + 1300] = 0
+    ref = torch.randn(1600, 2000, device=cuda_device, generator=torch.Generator(device=cuda_device).manual_seed(9 + knob))
+    ref[128:128 + 1300, 512:512 + 1300] = 0
+    assert torch.equal(outside, ref)                                   # nothing outside the block was written
+
+
 @pytest.mark.parametrize("shape", [(257, 256, 128), (300, 1000, 1024), (1024, 4096, 4096), (2048, 520, 14336)])
 def test_pair_kernel_w4a16_matches_the_one_cta_kernel(cuda_device, pair_knob, shape):
     """W4A16 prefill through the two-CTA kernel (each CTA unpacks its 128 of the tile's 256 weight rows) against the one-CTA
