@@ -184,6 +184,10 @@ template <> struct Vec16<CFB200_F32> {
 };
 template <> struct Vec16<CFB200_BF16> {
   static constexpr int kElems = 8;
+  typedef __nv_bfloat162 Pair2;  // two elements of a 32-bit word (low half = the earlier element)
+  static __device__ __forceinline__ Pair2 zero2() { return __floats2bfloat162_rn(0.0f, 0.0f); }
+  static __device__ __forceinline__ float low_f32(Pair2 p) { return __uint_as_float(*reinterpret_cast<const uint32_t*>(&p) << 16); }
+  static __device__ __forceinline__ float high_f32(Pair2 p) { return __uint_as_float(*reinterpret_cast<const uint32_t*>(&p) & 0xffff0000u); }
   static __device__ __forceinline__ void unpack(uint4 r, float* f) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
@@ -195,6 +199,10 @@ template <> struct Vec16<CFB200_BF16> {
 };
 template <> struct Vec16<CFB200_F16> {
   static constexpr int kElems = 8;
+  typedef __half2 Pair2;
+  static __device__ __forceinline__ Pair2 zero2() { return __floats2half2_rn(0.0f, 0.0f); }
+  static __device__ __forceinline__ float low_f32(Pair2 p) { return __low2float(p); }
+  static __device__ __forceinline__ float high_f32(Pair2 p) { return __high2float(p); }
   static __device__ __forceinline__ void unpack(uint4 r, float* f) {
     const uint32_t w[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll

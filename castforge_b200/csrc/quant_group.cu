@@ -726,6 +726,47 @@ quant_int4_asym_kernel(const void* __restrict__ src, size_t n, uint8_t* __restri
         for (int k = 0; k < NW; ++k) raw[it][k] = nxt[it][k];
       }
       if (pr + w.warps_total < full_pairs) prefetch(pr + w.warps_total);  // the next trip's loads fly under this trip's math
+      // ---- ranges of the trip's kItems groups ----
+      float glo[kItems], ghi[kItems];
+#pragma unroll
+      for (int it = 0; it < kItems; ++it) {
+        float lo = 0.0f, hi = 0.0f;  // the range always contains 0
+        if constexpr (kF32) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) { lo = fminf(lo, __uint_as_float(raw[it][k])); hi = fmaxf(hi, __uint_as_float(raw[it][k])); }
+        } else {
+          // two elements per instruction on the packed 16-bit values (a NaN operand is ignored, as fminf / fmaxf do);
+          // widening the two winners is exact
+          typedef typename Vec16<DT>::Pair2 P2;
+          P2 lo2 = Vec16<DT>::zero2(), hi2 = lo2;
+#pragma unroll
+          for (int k = 0; k < NW; ++k) {
+            const P2 v2 = *reinterpret_cast<const P2*>(&raw[it][k]);
+            lo2 = __hmin2(lo2, v2);
+            hi2 = __hmax2(hi2, v2);
+          }
+          lo = fminf(Vec16<DT>::low_f32(lo2), Vec16<DT>::high_f32(lo2));
+          hi = fmaxf(Vec16<DT>::low_f32(hi2), Vec16<DT>::high_f32(hi2));
+        }
+        glo[it] = group_min<LPG>(lo);
+        ghi[it] = group_max<LPG>(hi);
+      }
+      // ---- scale, its reciprocal and the zero point: ONE pass of the scalar arithmetic (three IEEE divisions, the f16
+      // truncation, the rounding) serves all kItems groups, lane j of a group working for item j mod kItems ----
+      static_assert((kItems & (kItems - 1)) == 0 && kItems <= LPG, "items per trip: a power of two, at most the lanes of a group");
+      const int mine = w.lane & (kItems - 1);
+      float mlo = glo[0], mhi = ghi[0];
+#pragma unroll
+      for (int it = 1; it < kItems; ++it) {
+        mlo = (mine == it) ? glo[it] : mlo;
+        mhi = (mine == it) ? ghi[it] : mhi;
+      }
+      const unsigned my_sh = f16_trunc_scale_bits(__fdiv_rn(__fsub_rn(mhi, mlo), 15.0f));
+      const float my_s = __half2float(__ushort_as_half((unsigned short)my_sh));
+      const float my_inv = __fdiv_rn(1.0f, my_s);
+      const float my_zf = keep_nan_clamp(roundf(__fdiv_rn(-mlo, my_s)), 0.0f, 15.0f);
+      const int my_zp = clamp_to_int(my_zf, 0.0f, 15.0f);
+      const int gbase = w.lane & ~(LPG - 1);
 #pragma unroll
       for (int it = 0; it < kItems; ++it) {
         float f[EPL];
@@ -741,16 +782,10 @@ quant_int4_asym_kernel(const void* __restrict__ src, size_t n, uint8_t* __restri
             for (int k = 0; k < 8; ++k) f[8 * v + k] = t[k];
           }
         }
-        float lo = 0.0f, hi = 0.0f;  // the range always contains 0
-#pragma unroll
-        for (int k = 0; k < EPL; ++k) { lo = fminf(lo, f[k]); hi = fmaxf(hi, f[k]); }
-        lo = group_min<LPG>(lo);
-        hi = group_max<LPG>(hi);
-        const unsigned sh = f16_trunc_scale_bits(__fdiv_rn(__fsub_rn(hi, lo), 15.0f));
-        const float s = __half2float(__ushort_as_half((unsigned short)sh));
-        const float inv = __fdiv_rn(1.0f, s);
-        const float zf = keep_nan_clamp(roundf(__fdiv_rn(-lo, s)), 0.0f, 15.0f);
-        zp[it] = clamp_to_int(zf, 0.0f, 15.0f);
+        const float s = __shfl_sync(kFullMask, my_s, gbase + it);
+        const float inv = __shfl_sync(kFullMask, my_inv, gbase + it);
+        const float zf = __shfl_sync(kFullMask, my_zf, gbase + it);
+        zp[it] = __shfl_sync(kFullMask, my_zp, gbase + it);
         // q = clamp(round(v/s) + zp, 0, 15) = round(clamp(v/s, -zp, 15-zp)) + zp: the bounds are
         // integers and rounding is monotone.  fmaxf first: a NaN quotient becomes -zp -> code 0,
         // which is what `NaN as u8` gives in the reference formula.
@@ -778,7 +813,7 @@ quant_int4_asym_kernel(const void* __restrict__ src, size_t n, uint8_t* __restri
         }
         if constexpr (EPL == 16) st_stream8(codes + (e0[it] >> 1), make_uint2(nib[0], nib[1]));
         else st_stream4(codes + (e0[it] >> 1), nib[0]);
-        if ((w.lane % LPG) == 0) scales[e0[it] / G] = (uint16_t)sh;
+        if ((w.lane % LPG) == it) scales[e0[it] / G] = (uint16_t)my_sh;  // the lane that worked for this item holds its scale
       }
       if constexpr (LPG == 32) {
         const size_t g0 = e0[0] / G;
