@@ -985,11 +985,24 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 }
 
 // bf16 -> f16 (round to nearest, saturating at +-65504; NaN stays NaN) for the W4 mode's activations
+__device__ __forceinline__ __half bf16_to_f16_sat(__nv_bfloat16 b) {
+  const float v = __bfloat162float(b);
+  return __float2half_rn((v != v) ? v : fminf(fmaxf(v, -65504.0f), 65504.0f));
+}
 __global__ void bf16_to_f16_kernel(const __nv_bfloat16* __restrict__ x, size_t n, __half* __restrict__ out) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const float v = __bfloat162float(x[i]);
-    out[i] = __float2half_rn((v != v) ? v : fminf(fmaxf(v, -65504.0f), 65504.0f));
+  // eight elements (16 bytes in, 16 bytes out) per thread and trip when the source is 16-byte aligned (the workspace is)
+  const size_t n8 = (reinterpret_cast<uintptr_t>(x) & 15) == 0 ? n / 8 : 0;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 r = __ldg(reinterpret_cast<const uint4*>(x) + i);
+    const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&r);
+    uint4 o;
+    __half* h = reinterpret_cast<__half*>(&o);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) h[k] = bf16_to_f16_sat(b[k]);
+    reinterpret_cast<uint4*>(out)[i] = o;
   }
+  for (size_t i = n8 * 8 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+    out[i] = bf16_to_f16_sat(x[i]);
 }
 
 // The same staging pass with castforge.static_quantize (src/codegen/eval.rs:1369-1382) applied on the way: the f32 value
@@ -1283,7 +1296,8 @@ int32_t gemm_w4a16_impl(const void* A, int a_mode, float a_scale, int a_bits, co
   size_t blocks = (n + 255) / 256, cap = (size_t)sm_count() * 16;
   const unsigned cgrid = (unsigned)(blocks < cap ? blocks : cap);
   if (a_mode == 0) {
-    bf16_to_f16_kernel<<<cgrid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(A), n, reinterpret_cast<__half*>(workspace));
+    const size_t vblocks = (n / 8 + 255) / 256 + 1;
+    bf16_to_f16_kernel<<<(unsigned)(vblocks < cap ? vblocks : cap), 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(A), n, reinterpret_cast<__half*>(workspace));
   } else {
     const float sc = a_scale > 0.0f ? a_scale : 1.0f / 127.0f;  // the interpreter's default for a missing scale attribute
     const float qmax = a_bits == 4 ? 7.0f : 127.0f;
