@@ -191,6 +191,61 @@ __device__ __forceinline__ uint32_t make_idesc(int mma_m, int mma_n) {
 // the kernel
 // ---------------------------------------------------------------------------------------------
 // AM: 128-row A tiles per CTA (1 or 2).  With 2, a B tile -- in the W4 mode an unpacked one -- feeds two accumulators.
+// 32 accumulator columns of one output row -> C (scales, output format, optional C +=)
+__device__ __forceinline__ void store_row32(const GemmArgs& args, int row, int col0, const uint32_t (&r)[32], float rs) {
+  if (args.out_f32) {
+    float* dst = reinterpret_cast<float*>(args.C) + (size_t)row * args.ldc + col0;
+    if (col0 + 32 <= args.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+      float4* d4 = reinterpret_cast<float4*>(dst);
+      float4 o[8];
+      if (args.accumulate) {  // all eight loads of the old values first: behind each other's stores they would run one memory latency at a time
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __ldcg(d4 + j);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float4 v;
+        v.x = __uint_as_float(r[4 * j]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j] : 1.0f);
+        v.y = __uint_as_float(r[4 * j + 1]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j + 1] : 1.0f);
+        v.z = __uint_as_float(r[4 * j + 2]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j + 2] : 1.0f);
+        v.w = __uint_as_float(r[4 * j + 3]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j + 3] : 1.0f);
+        if (args.accumulate) {
+          v.x = __fadd_rn(o[j].x, v.x); v.y = __fadd_rn(o[j].y, v.y); v.z = __fadd_rn(o[j].z, v.z); v.w = __fadd_rn(o[j].w, v.w);
+        }
+        d4[j] = v;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < args.N) {
+          const float v = __uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f);
+          dst[j] = args.accumulate ? __fadd_rn(dst[j], v) : v;
+        }
+    }
+  } else {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(args.C) + (size_t)row * args.ldc + col0;
+    if (col0 + 32 <= args.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int tt = 0; tt < 4; ++tt) {
+          const float v0 = __uint_as_float(r[j + 2 * tt]) * rs * (args.col_scale ? args.col_scale[col0 + j + 2 * tt] : 1.0f);
+          const float v1 = __uint_as_float(r[j + 2 * tt + 1]) * rs * (args.col_scale ? args.col_scale[col0 + j + 2 * tt + 1] : 1.0f);
+          const __nv_bfloat162 b2 = __floats2bfloat162_rn(v0, v1);
+          pk[tt] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+        *reinterpret_cast<uint4*>(dst + j) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (col0 + j < args.N)
+          dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f));
+    }
+  }
+}
+
 #ifdef CFB_GEMM_TRACE
 // Cycle accounting of CTA 0's warps, for builds made with -DCFB_GEMM_TRACE only.
 // Every thread sums into registers; lane 0 of each warp of CTAs 0 and 1 writes its eight sums when the kernel ends.
@@ -501,41 +556,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const int col0 = n0 + c0;
           if (S > 1) {  // raw partial sums of this k slice; scales and the output format are applied by the reduction
             float* dst = args.partial + ((size_t)slice * args.M + row) * args.N + col0;
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < args.N) dst[j] = __uint_as_float(r[j]);
-          } else if (args.out_f32) {
-            float* dst = reinterpret_cast<float*>(args.C) + (size_t)row * args.ldc + col0;
-            if (args.accumulate) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < args.N) dst[j] = __fadd_rn(dst[j], __uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f));
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (col0 + j < args.N) dst[j] = __uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f);
-            }
-          } else {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(args.C) + (size_t)row * args.ldc + col0;
             if (col0 + 32 <= args.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint32_t pk[4];
-#pragma unroll
-                for (int tt = 0; tt < 4; ++tt) {
-                  const float v0 = __uint_as_float(r[j + 2 * tt]) * rs * (args.col_scale ? args.col_scale[col0 + j + 2 * tt] : 1.0f);
-                  const float v1 = __uint_as_float(r[j + 2 * tt + 1]) * rs * (args.col_scale ? args.col_scale[col0 + j + 2 * tt + 1] : 1.0f);
-                  const __nv_bfloat162 b2 = __floats2bfloat162_rn(v0, v1);
-                  pk[tt] = *reinterpret_cast<const uint32_t*>(&b2);
-                }
-                *reinterpret_cast<uint4*>(dst + j) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-              }
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]),
+                                                                  __uint_as_float(r[j + 3]));
             } else {
 #pragma unroll
               for (int j = 0; j < 32; ++j)
-                if (col0 + j < args.N)
-                  dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f));
+                if (col0 + j < args.N) dst[j] = __uint_as_float(r[j]);
             }
+          } else if (col0 < args.N) {
+            store_row32(args, row, col0, r, rs);
           }
         }
       }
@@ -647,61 +679,6 @@ __device__ __forceinline__ void tcgen05_mma_pair(uint32_t tmem_d, uint64_t desc_
         "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
         "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
-  }
-}
-
-// 32 accumulator columns of one output row -> C (scales, output format, optional C +=)
-__device__ __forceinline__ void store_row32(const GemmArgs& args, int row, int col0, const uint32_t (&r)[32], float rs) {
-  if (args.out_f32) {
-    float* dst = reinterpret_cast<float*>(args.C) + (size_t)row * args.ldc + col0;
-    if (col0 + 32 <= args.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-      float4* d4 = reinterpret_cast<float4*>(dst);
-      float4 o[8];
-      if (args.accumulate) {  // all eight loads of the old values first: behind each other's stores they would run one memory latency at a time
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = __ldcg(d4 + j);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float4 v;
-        v.x = __uint_as_float(r[4 * j]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j] : 1.0f);
-        v.y = __uint_as_float(r[4 * j + 1]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j + 1] : 1.0f);
-        v.z = __uint_as_float(r[4 * j + 2]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j + 2] : 1.0f);
-        v.w = __uint_as_float(r[4 * j + 3]) * rs * (args.col_scale ? args.col_scale[col0 + 4 * j + 3] : 1.0f);
-        if (args.accumulate) {
-          v.x = __fadd_rn(o[j].x, v.x); v.y = __fadd_rn(o[j].y, v.y); v.z = __fadd_rn(o[j].z, v.z); v.w = __fadd_rn(o[j].w, v.w);
-        }
-        d4[j] = v;
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < args.N) {
-          const float v = __uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f);
-          dst[j] = args.accumulate ? __fadd_rn(dst[j], v) : v;
-        }
-    }
-  } else {
-    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(args.C) + (size_t)row * args.ldc + col0;
-    if (col0 + 32 <= args.N && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-      for (int j = 0; j < 32; j += 8) {
-        uint32_t pk[4];
-#pragma unroll
-        for (int tt = 0; tt < 4; ++tt) {
-          const float v0 = __uint_as_float(r[j + 2 * tt]) * rs * (args.col_scale ? args.col_scale[col0 + j + 2 * tt] : 1.0f);
-          const float v1 = __uint_as_float(r[j + 2 * tt + 1]) * rs * (args.col_scale ? args.col_scale[col0 + j + 2 * tt + 1] : 1.0f);
-          const __nv_bfloat162 b2 = __floats2bfloat162_rn(v0, v1);
-          pk[tt] = *reinterpret_cast<const uint32_t*>(&b2);
-        }
-        *reinterpret_cast<uint4*>(dst + j) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (col0 + j < args.N)
-          dst[j] = __float2bfloat16_rn(__uint_as_float(r[j]) * rs * (args.col_scale ? args.col_scale[col0 + j] : 1.0f));
-    }
   }
 }
 
