@@ -124,10 +124,26 @@ __device__ __forceinline__ float ld_dsmem_f32(const float* local, uint32_t rank)
 
 // grid.x = clusters * csize.  A cluster owns kWarps * tiles_per_warp tiles of 16 output channels;
 // CTA `rank` of the cluster owns chunks [rank*cpc, rank*cpc + cpc) of K for all of them.
+#ifdef CFB_GV_TRACE
+// wall-clock stamps (%globaltimer, ns) of every CTA of the register-ring kernel, for builds made with -DCFB_GV_TRACE only
+__device__ unsigned long long g_gvstamp[1024 * 4];
+__device__ __forceinline__ void gv_stamp(int slot) {
+  if (threadIdx.x == 0 && blockIdx.x < 1024) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    g_gvstamp[blockIdx.x * 4 + slot] = t;
+  }
+}
+#define GV_STAMP(slot) gv_stamp(slot)
+#else
+#define GV_STAMP(slot) do { } while (0)
+#endif
+
 template <int MT>
 __global__ void __launch_bounds__(kThreadsGv)
 gemv_w4_kernel(const GvArgs a, int tiles_per_warp, int cpc /* chunks per CTA */, int pitch, int csize /* CTAs per cluster */) {
   extern __shared__ __align__(128) uint8_t smem[];
+  GV_STAMP(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const uint32_t rank = cluster_rank();
   const int cluster_id = blockIdx.x / csize;
@@ -173,6 +189,7 @@ gemv_w4_kernel(const GvArgs a, int tiles_per_warp, int cpc /* chunks per CTA */,
   // the first weights are on their way while the activations are staged
   stage_acts<MT>(a, smem, c0, cpc, pitch);
   __syncthreads();
+  GV_STAMP(1);
   for (int it0 = 0; it0 < nitems; it0 += kDepth) {
 #pragma unroll
     for (int d = 0; d < kDepth; ++d) {
@@ -217,6 +234,7 @@ gemv_w4_kernel(const GvArgs a, int tiles_per_warp, int cpc /* chunks per CTA */,
   }
 
   // this CTA's partial sums -> its own shared memory, then the cluster adds them up over DSMEM
+  GV_STAMP(2);
 #pragma unroll
   for (int ti = 0; ti < kMaxTiles; ++ti) {
     if (ti >= tiles_per_warp) break;
@@ -246,6 +264,7 @@ gemv_w4_kernel(const GvArgs a, int tiles_per_warp, int cpc /* chunks per CTA */,
     }
   }
   if (csize > 1) cluster_sync_all();  // nobody leaves while its shared memory may still be read
+  GV_STAMP(3);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -697,6 +716,17 @@ int32_t read_gv_flag(int* out) {
 }  // namespace cfb
 
 using namespace cfb;
+
+#ifdef CFB_GV_TRACE
+extern "C" int32_t cfb200_debug_gv_trace(unsigned long long* out, int reset) {
+  if (out && cudaMemcpyFromSymbol(out, g_gvstamp, sizeof(g_gvstamp)) != cudaSuccess) return 1;
+  if (reset) {
+    static unsigned long long z[1024 * 4];
+    if (cudaMemcpyToSymbol(g_gvstamp, z, sizeof(z)) != cudaSuccess) return 1;
+  }
+  return 0;
+}
+#endif
 
 extern "C" int32_t cfb200_gemv_w4a16(const void* A, const uint8_t* w_codes, const uint16_t* w_scales, const uint8_t* w_zps,
                                      size_t M, size_t N, size_t K, size_t group, void* C, int32_t out_f32, void* stream) {
