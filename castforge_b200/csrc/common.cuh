@@ -36,7 +36,7 @@ enum Tunable {
 long long tunable(int id);
 // Give-up-path self-tests (a short bounded wait on a barrier nothing completes): what the host then observes.
 int32_t a1_expired_wait_selftest(int32_t* observed);
-int32_t tc_expired_wait_selftest(int32_t* observed);
+int32_t tc_expired_wait_selftest(int32_t* observed, int which);
 
 #define CFB_CHECK_ARG(cond, ...)                                        \
   do {                                                                  \

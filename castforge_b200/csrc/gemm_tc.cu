@@ -99,8 +99,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* er
 
 // the same bounded wait for a warp that expects to wait long (an epilogue warp during a tile's main loop): it sleeps
 // between polls and leaves the issue slots of its scheduler to the warps that feed the tensor core
-__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, int* error_flag, int code, volatile int* s_abort) {
-  for (unsigned i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, int* error_flag, int code, volatile int* s_abort,
+                                               unsigned limit = kSpinLimit) {
+  for (unsigned i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     __nanosleep(64);
     if ((i & 1023u) == 1023u && *s_abort) return false;
@@ -634,8 +635,9 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* error_flag, int code, volatile int* s_abort) {
-  for (unsigned i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, int* error_flag, int code, volatile int* s_abort,
+                                                  unsigned limit = kSpinLimit) {
+  for (unsigned i = 0; i < limit; ++i) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *s_abort) return false;
   }
@@ -1117,22 +1119,25 @@ namespace cfb {
 namespace {
 // Self-test of the give-up path of the tensor-core kernels: the same bounded wait on a barrier that nothing completes,
 // with a short limit; the caller's error word receives the code, as it does from a kernel.
-__global__ void tc_wait_probe_kernel(int* error_flag, unsigned limit) {
+// which: 0 = the plain wait, 1 = the sleeping wait of the epilogue warps, 2 = the wait that sees the other CTA's arrivals
+__global__ void tc_wait_probe_kernel(int* error_flag, unsigned limit, int which) {
   __shared__ __align__(8) uint64_t s_bar;
   __shared__ int s_abort;
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(smem_u32(&s_bar), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    mbar_wait(smem_u32(&s_bar), 0u, error_flag, 7, &s_abort, limit);
+    if (which == 0) mbar_wait(smem_u32(&s_bar), 0u, error_flag, 7, &s_abort, limit);
+    else if (which == 1) mbar_wait_idle(smem_u32(&s_bar), 0u, error_flag, 8, &s_abort, limit);
+    else mbar_wait_cluster(smem_u32(&s_bar), 0u, error_flag, 9, &s_abort, limit);
   }
 }
 }  // namespace
-int32_t tc_expired_wait_selftest(int32_t* observed) {
+int32_t tc_expired_wait_selftest(int32_t* observed, int which) {
   int* flag = nullptr;
   CFB_CUDA(cudaMalloc(&flag, sizeof(int)));
   cudaMemset(flag, 0, sizeof(int));
-  tc_wait_probe_kernel<<<1, 32>>>(flag, 1u << 12);
+  tc_wait_probe_kernel<<<1, 32>>>(flag, 1u << 12, which);
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess) e = cudaMemcpy(observed, flag, sizeof(int), cudaMemcpyDeviceToHost);
   cudaFree(flag);

@@ -50,7 +50,7 @@ extern "C" int32_t cfb200_selftest_expired_wait(int32_t which, int32_t* observed
   if (!observed_host) return cfb::set_error(CFB200_ERR_INVALID, "NULL argument");
   *observed_host = 0;
   if (which == 0) return cfb::a1_expired_wait_selftest(observed_host);
-  if (which == 1) return cfb::tc_expired_wait_selftest(observed_host);
+  if (which >= 1 && which <= 3) return cfb::tc_expired_wait_selftest(observed_host, which - 1);
   return cfb::set_error(CFB200_ERR_INVALID, "unknown self-test %d", which);
 }
 

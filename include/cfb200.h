@@ -107,8 +107,10 @@ int32_t cfb200_quant_sym_status(int32_t* flag_host);
  * few thousand polls, on a barrier that nothing completes, gives up and reports exactly as the real kernels do:
  * which == 0: through the sticky flag of the cooperative A1 launch -- *observed_host receives what
  * cfb200_quant_sym_status then reads (1), and the flag is cleared again; which == 1: through a caller error word as
- * the tensor-core GEMMs use it -- *observed_host receives the code written there (7).  Touches no caller memory,
- * leaves nothing in flight, runs in microseconds.  (which == 1 allocates and frees four bytes of device memory.) */
+ * the tensor-core GEMMs use it -- *observed_host receives the code written there (7); which == 2 and 3: the same for
+ * the two other waits of the pair kernel (the sleeping wait of its epilogue warps, code 8; the wait that observes the
+ * other CTA's arrivals, code 9).  Touches no caller memory, leaves nothing in flight, runs in microseconds.
+ * (which >= 1 allocates and frees four bytes of device memory.) */
 int32_t cfb200_selftest_expired_wait(int32_t which, int32_t* observed_host);
 
 /* ---- A6: per-tensor fake quantization (QAT-STE) --------------------------------------------

@@ -226,4 +226,6 @@ def test_bounded_waits_give_up_and_report(cuda_device):
     flag = ctypes.c_int32(-1)
     assert lib.cfb200_quant_sym_status(ctypes.byref(flag)) == 0 and flag.value == 0      # cleared: later runs start clean
     assert lib.cfb200_selftest_expired_wait(1, ctypes.byref(seen)) == 0 and seen.value == 7
+    assert lib.cfb200_selftest_expired_wait(2, ctypes.byref(seen)) == 0 and seen.value == 8      # the pair kernel's sleeping wait
+    assert lib.cfb200_selftest_expired_wait(3, ctypes.byref(seen)) == 0 and seen.value == 9      # ... and its cluster-scope wait
     assert lib.cfb200_selftest_expired_wait(9, ctypes.byref(seen)) == 1
