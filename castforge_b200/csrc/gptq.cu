@@ -49,11 +49,17 @@ __global__ void transpose_bf16_kernel(const __nv_bfloat16* __restrict__ in, size
 
 // ---- generic f32 GEMM: C[m,n] = beta*C[m,n] + alpha * sum_k A(m,k) * B(k,n), element strides ------
 // 128 x 128 tile per CTA, 8 x 8 outputs per thread (two 4-wide halves 64 apart, so that the shared-memory reads are
-// conflict-free 16-byte loads), k-tile 16, the next k-tile's global loads in flight while the current one is multiplied.
-// Operands are addressed through (row stride, column stride) so that transposes cost nothing; consecutive threads
-// walk whichever of the two dimensions is contiguous in memory.
+// conflict-free 16-byte loads), k-tile 16 in two shared-memory buffers (one barrier per k-tile), the next k-tile's global
+// loads in flight while the current one is multiplied.  Operands are addressed through (row stride, column stride) so that
+// transposes cost nothing; a thread fetches four consecutive elements along whichever dimension is contiguous in memory
+// with one 16-byte load where the tile lies inside the operand and the addresses allow it.  Every output element is one
+// chain of fused multiply-adds in ascending k, whatever path its operands took.
 constexpr int kSgBM = 128, kSgBN = 128, kSgBK = 16;
 
+// FLUSH > 0 (a multiple of the k-tile; beta = 1): the sum restarts every FLUSH values of k and each partial sum goes into C
+// with its own rounded addition, C = C + alpha * partial, exactly as K / FLUSH separate calls with K = FLUSH would leave
+// it -- but C is read and written once.  The running C values live in registers meanwhile.
+template <int FLUSH>
 __global__ void __launch_bounds__(256)
 sgemm_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, long rsA, long csA, const float* __restrict__ B,
              long rsB, long csB, float beta, float* __restrict__ C, long ldc, int mode, long batchA, long batchB, long batchC) {
@@ -61,7 +67,7 @@ sgemm_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, long
   B += (long)blockIdx.z * batchB;
   C += (long)blockIdx.z * batchC;
   // rows padded by 4 floats: a k-fast operand is stored 16 k apart per thread, which would hit one bank without it
-  __shared__ __align__(16) float sA[kSgBK][kSgBM + 4], sB[kSgBK][kSgBN + 4];
+  __shared__ __align__(16) float sA[2][kSgBK][kSgBM + 4], sB[2][kSgBK][kSgBN + 4];
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * kSgBM, n0 = blockIdx.x * kSgBN;
   // mode bit 0: only tiles that touch the lower triangle of C are wanted (symmetric update);
@@ -70,40 +76,116 @@ sgemm_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, long
   if ((mode & 1) && n0 > m0 + kSgBM - 1) return;
   const int k_begin = (mode & 2) ? (n0 / kSgBK) * kSgBK : 0;
   if (mode & 4) K = min(K, m0 + kSgBM);
-  // element e of a tile (e = 0 .. 2047): (mm, kk) with the contiguous dimension fastest
   const bool a_m_fast = (rsA == 1), b_n_fast = (csB == 1);
+  // 16-byte loads: the operand's contiguous dimension has stride 1, the other stride and the base keep 16-byte alignment,
+  // and the tile's rows / columns all exist (k is checked per k-tile)
+  const bool a_vec = (a_m_fast ? (csA % 4 == 0) : (csA == 1 && rsA % 4 == 0)) && ((reinterpret_cast<uintptr_t>(A) & 15) == 0) && m0 + kSgBM <= M;
+  const bool b_vec = (b_n_fast ? (rsB % 4 == 0) : (rsB == 1 && csB % 4 == 0)) && ((reinterpret_cast<uintptr_t>(B) & 15) == 0) && n0 + kSgBN <= N;
+  // a tile of an operand is 128 (m or n) x 16 (k) = 2048 elements = 512 groups of four along the contiguous dimension:
+  // two groups per thread.  Group q: along-m/n-fast: (kk = q / 32, mm = 4 * (q % 32)); k-fast: (mm = q / 4, kk = 4 * (q % 4)).
+  float4 va[2], vb[2];
   float ra[8], rb[8];
+  bool a_v = false, b_v = false;  // how the tile in flight was fetched
   auto gload = [&](int k0) {
+    a_v = a_vec && k0 + kSgBK <= K;
+    b_v = b_vec && k0 + kSgBK <= K;
+    if (a_v) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int e = tid + i * 256;
-      const int amm = a_m_fast ? (e & 127) : (e >> 4), akk = a_m_fast ? (e >> 7) : (e & 15);
-      ra[i] = (m0 + amm < M && k0 + akk < K) ? A[(long)(m0 + amm) * rsA + (long)(k0 + akk) * csA] : 0.0f;
-      const int bnn = b_n_fast ? (e & 127) : (e >> 4), bkk = b_n_fast ? (e >> 7) : (e & 15);
-      rb[i] = (n0 + bnn < N && k0 + bkk < K) ? B[(long)(k0 + bkk) * rsB + (long)(n0 + bnn) * csB] : 0.0f;
+      for (int u = 0; u < 2; ++u) {
+        const int q = tid + u * 256;
+        const int mm = a_m_fast ? 4 * (q & 31) : (q >> 2), kk = a_m_fast ? (q >> 5) : 4 * (q & 3);
+        va[u] = *reinterpret_cast<const float4*>(A + (long)(m0 + mm) * rsA + (long)(k0 + kk) * csA);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = tid + i * 256;
+        const int amm = a_m_fast ? (e & 127) : (e >> 4), akk = a_m_fast ? (e >> 7) : (e & 15);
+        ra[i] = (m0 + amm < M && k0 + akk < K) ? A[(long)(m0 + amm) * rsA + (long)(k0 + akk) * csA] : 0.0f;
+      }
+    }
+    if (b_v) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int q = tid + u * 256;
+        const int nn = b_n_fast ? 4 * (q & 31) : (q >> 2), kk = b_n_fast ? (q >> 5) : 4 * (q & 3);
+        vb[u] = *reinterpret_cast<const float4*>(B + (long)(k0 + kk) * rsB + (long)(n0 + nn) * csB);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = tid + i * 256;
+        const int bnn = b_n_fast ? (e & 127) : (e >> 4), bkk = b_n_fast ? (e >> 7) : (e & 15);
+        rb[i] = (n0 + bnn < N && k0 + bkk < K) ? B[(long)(k0 + bkk) * rsB + (long)(n0 + bnn) * csB] : 0.0f;
+      }
     }
   };
-  auto sstore = [&]() {
+  auto sstore = [&](int buf) {
+    if (a_v) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int e = tid + i * 256;
-      const int amm = a_m_fast ? (e & 127) : (e >> 4), akk = a_m_fast ? (e >> 7) : (e & 15);
-      sA[akk][amm] = ra[i];
-      const int bnn = b_n_fast ? (e & 127) : (e >> 4), bkk = b_n_fast ? (e >> 7) : (e & 15);
-      sB[bkk][bnn] = rb[i];
+      for (int u = 0; u < 2; ++u) {
+        const int q = tid + u * 256;
+        if (a_m_fast) {
+          *reinterpret_cast<float4*>(&sA[buf][q >> 5][4 * (q & 31)]) = va[u];
+        } else {
+          const int mm = q >> 2, kk = 4 * (q & 3);
+          sA[buf][kk][mm] = va[u].x; sA[buf][kk + 1][mm] = va[u].y; sA[buf][kk + 2][mm] = va[u].z; sA[buf][kk + 3][mm] = va[u].w;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = tid + i * 256;
+        const int amm = a_m_fast ? (e & 127) : (e >> 4), akk = a_m_fast ? (e >> 7) : (e & 15);
+        sA[buf][akk][amm] = ra[i];
+      }
+    }
+    if (b_v) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int q = tid + u * 256;
+        if (b_n_fast) {
+          *reinterpret_cast<float4*>(&sB[buf][q >> 5][4 * (q & 31)]) = vb[u];
+        } else {
+          const int nn = q >> 2, kk = 4 * (q & 3);
+          sB[buf][kk][nn] = vb[u].x; sB[buf][kk + 1][nn] = vb[u].y; sB[buf][kk + 2][nn] = vb[u].z; sB[buf][kk + 3][nn] = vb[u].w;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int e = tid + i * 256;
+        const int bnn = b_n_fast ? (e & 127) : (e >> 4), bkk = b_n_fast ? (e >> 7) : (e & 15);
+        sB[buf][bkk][bnn] = rb[i];
+      }
     }
   };
   float acc[8][8] = {};
-  gload(k_begin);
+  float crun[FLUSH > 0 ? 8 : 1][FLUSH > 0 ? 8 : 1];
+  if (FLUSH > 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+        crun[FLUSH > 0 ? i : 0][FLUSH > 0 ? j : 0] = (m < M && n < N) ? C[(long)m * ldc + n] : 0.0f;
+      }
+    }
+  }
+  int buf = 0;
+  if (k_begin < K) {
+    gload(k_begin);
+    sstore(0);
+  }
+  __syncthreads();
   for (int k0 = k_begin; k0 < K; k0 += kSgBK) {
-    __syncthreads();  // the previous tile has been read by everyone
-    sstore();
-    __syncthreads();
-    if (k0 + kSgBK < K) gload(k0 + kSgBK);
+    const bool more = k0 + kSgBK < K;
+    if (more) gload(k0 + kSgBK);
 #pragma unroll
     for (int kk = 0; kk < kSgBK; ++kk) {
-      const float4 a0 = *reinterpret_cast<const float4*>(&sA[kk][ty * 4]), a1 = *reinterpret_cast<const float4*>(&sA[kk][64 + ty * 4]);
-      const float4 b0 = *reinterpret_cast<const float4*>(&sB[kk][tx * 4]), b1 = *reinterpret_cast<const float4*>(&sB[kk][64 + tx * 4]);
+      const float4 a0 = *reinterpret_cast<const float4*>(&sA[buf][kk][ty * 4]), a1 = *reinterpret_cast<const float4*>(&sA[buf][kk][64 + ty * 4]);
+      const float4 b0 = *reinterpret_cast<const float4*>(&sB[buf][kk][tx * 4]), b1 = *reinterpret_cast<const float4*>(&sB[buf][kk][64 + tx * 4]);
       const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
       const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
@@ -111,6 +193,19 @@ sgemm_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, long
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
     }
+    if (FLUSH > 0 && (k0 + kSgBK) % (FLUSH > 0 ? FLUSH : 1) == 0) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float& cr = crun[FLUSH > 0 ? i : 0][FLUSH > 0 ? j : 0];
+          cr = beta * cr + alpha * acc[i][j];
+          acc[i][j] = 0.0f;
+        }
+    }
+    if (more) sstore(buf ^ 1);  // the other buffer: everyone left it at the previous barrier
+    __syncthreads();
+    buf ^= 1;
   }
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
@@ -121,17 +216,20 @@ sgemm_kernel(int M, int N, int K, float alpha, const float* __restrict__ A, long
       const int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
       if (n < N) {
         float* c = C + (long)m * ldc + n;
-        *c = (beta == 0.0f ? 0.0f : beta * *c) + alpha * acc[i][j];
+        if (FLUSH > 0) *c = crun[FLUSH > 0 ? i : 0][FLUSH > 0 ? j : 0];
+        else *c = (beta == 0.0f ? 0.0f : beta * *c) + alpha * acc[i][j];
       }
     }
   }
 }
 
 void sgemm(cudaStream_t st, int M, int N, int K, float alpha, const float* A, long rsA, long csA, const float* B, long rsB, long csB,
-           float beta, float* C, long ldc, int mode = 0, int batch = 1, long batchA = 0, long batchB = 0, long batchC = 0) {
+           float beta, float* C, long ldc, int mode = 0, int batch = 1, long batchA = 0, long batchB = 0, long batchC = 0,
+           int flush = 0) {
   if (M <= 0 || N <= 0 || batch <= 0) return;
   dim3 grid((N + kSgBN - 1) / kSgBN, (M + kSgBM - 1) / kSgBM, batch);
-  sgemm_kernel<<<grid, 256, 0, st>>>(M, N, K, alpha, A, rsA, csA, B, rsB, csB, beta, C, ldc, mode, batchA, batchB, batchC);
+  if (flush == 128) sgemm_kernel<128><<<grid, 256, 0, st>>>(M, N, K, alpha, A, rsA, csA, B, rsB, csB, beta, C, ldc, mode, batchA, batchB, batchC);
+  else sgemm_kernel<0><<<grid, 256, 0, st>>>(M, N, K, alpha, A, rsA, csA, B, rsB, csB, beta, C, ldc, mode, batchA, batchB, batchC);
 }
 
 // ---- small helpers on K x K matrices ---------------------------------------------------------------
@@ -343,7 +441,7 @@ __device__ __forceinline__ unsigned f16_trunc_scale_bits(float v) {
 // One block of 128 columns starting at column b.  Warp per row; lane l holds columns l, l+32, l+64, l+96.
 __global__ void __launch_bounds__(256)
 gptq_block_kernel(float* __restrict__ W, int N, int K, int b, const float* __restrict__ U, uint8_t* __restrict__ codes,
-                  uint16_t* __restrict__ scales, uint8_t* __restrict__ zp_bytes, float* __restrict__ Err) {
+                  uint16_t* __restrict__ scales, uint8_t* __restrict__ zp_bytes, float* __restrict__ Err, int err_pitch) {
   extern __shared__ float su[];  // U[b..b+128)[b..b+128), row-major, pitch 129
   for (int i = threadIdx.x; i < 128 * 128; i += 256) {
     const int r = i >> 7, c = i & 127;
@@ -390,7 +488,7 @@ gptq_block_kernel(float* __restrict__ W, int N, int K, int b, const float* __res
     for (int s = 0; s < 4; ++s) {
       const int col = b + s * 32 + lane;
       W[(size_t)row * K + col] = w[s];  // the dequantised weight
-      Err[(size_t)row * 128 + s * 32 + lane] = e[s];
+      Err[(size_t)row * err_pitch + s * 32 + lane] = e[s];
       const int hi_n = __shfl_down_sync(kFullMask, q[s], 1);
       if ((lane & 1) == 0) codes[((size_t)row * K + col) >> 1] = (uint8_t)(q[s] | (hi_n << 4));
     }
@@ -596,7 +694,10 @@ extern "C" int32_t cfb200_gptq_prepare(const float* H, size_t K, float damp_rati
 }
 
 // Quantize W [N, K] (rows independent: a rank may own any row range).  workspace: N*K + N*128 floats + N*K/128 bytes.
-extern "C" size_t cfb200_gptq_quantize_workspace_bytes(size_t N, size_t K) { return (N * K + N * 128) * sizeof(float) + N * (K / 128) + 256; }
+constexpr size_t kWalkPanel = 1024;  // columns whose errors are kept before the columns right of them are updated
+extern "C" size_t cfb200_gptq_quantize_workspace_bytes(size_t N, size_t K) {
+  return (N * K + N * kWalkPanel) * sizeof(float) + N * (K / 128) + 256;
+}
 
 extern "C" int32_t cfb200_gptq_quantize(const void* W, int32_t w_dtype, size_t N, size_t K, const float* U, uint8_t* codes,
                                         uint16_t* scales, uint8_t* zero_points, float* w_dequant /* nullable, [N,K] f32 */,
@@ -609,7 +710,7 @@ extern "C" int32_t cfb200_gptq_quantize(const void* W, int32_t w_dtype, size_t N
   cudaStream_t st = (cudaStream_t)stream;
   float* Wf = reinterpret_cast<float*>(workspace);
   float* Err = Wf + N * K;
-  uint8_t* zpb = reinterpret_cast<uint8_t*>(Err + N * 128);
+  uint8_t* zpb = reinterpret_cast<uint8_t*>(Err + N * kWalkPanel);
   widen_kernel<<<2048, 256, 0, st>>>(W, w_dtype, N * K, Wf);
   static thread_local int attr_dev = -1;
   int dev = 0;
@@ -620,11 +721,24 @@ extern "C" int32_t cfb200_gptq_quantize(const void* W, int32_t w_dtype, size_t N
     attr_dev = dev;
   }
   const int grid = (int)std::min<size_t>((N + 7) / 8, (size_t)sm_count() * 3);
-  for (size_t b = 0; b < K; b += 128) {
-    gptq_block_kernel<<<grid, 256, smem, st>>>(Wf, (int)N, (int)K, (int)b, U, codes, scales, zpb, Err);
-    const size_t rest = K - b - 128;
-    if (rest > 0)  // W[:, b+128:] -= Err * U[b:b+128, b+128:]
-      sgemm(st, (int)N, (int)rest, 128, -1.0f, Err, 128, 1, U + b * K + b + 128, (long)K, 1, 1.0f, Wf + b + 128, (long)K);
+  // Every column block's errors reach every later column as ONE rounded subtraction of that block's 128-term sum, block
+  // after block (the order the CPU oracle repeats).  Inside a panel of kWalkPanel columns the columns still to be walked
+  // are updated after each block; the columns right of the panel get the panel's blocks in one launch that restarts its
+  // sum every 128 terms and subtracts each partial sum in turn -- the same operations in the same order, with one pass
+  // over those columns per panel instead of one per block.
+  for (size_t p0 = 0; p0 < K; p0 += kWalkPanel) {
+    const size_t p1 = std::min(K, p0 + kWalkPanel);
+    for (size_t b = p0; b < p1; b += 128) {
+      float* eb = Err + (b - p0);
+      gptq_block_kernel<<<grid, 256, smem, st>>>(Wf, (int)N, (int)K, (int)b, U, codes, scales, zpb, eb, (int)kWalkPanel);
+      const size_t c = p1 - b - 128;
+      if (c > 0)  // W[:, b+128 : p1] -= Err_b * U[b:b+128, b+128 : p1]
+        sgemm(st, (int)N, (int)c, 128, -1.0f, eb, (long)kWalkPanel, 1, U + b * K + b + 128, (long)K, 1, 1.0f, Wf + b + 128, (long)K);
+    }
+    const size_t rest = K - p1;
+    if (rest > 0)  // W[:, p1:] -= Err_b * U[b:b+128, p1:] for every block b of the panel, in order
+      sgemm(st, (int)N, (int)rest, (int)(p1 - p0), -1.0f, Err, (long)kWalkPanel, 1, U + p0 * K + p1, (long)K, 1, 1.0f, Wf + p1, (long)K, 0, 1, 0, 0,
+            0, 128);
   }
   pack_zp_kernel<<<256, 256, 0, st>>>(zpb, N * (K / 128), zero_points);
   if (w_dequant) CFB_CUDA(cudaMemcpyAsync(w_dequant, Wf, N * K * sizeof(float), cudaMemcpyDeviceToDevice, st));
