@@ -236,6 +236,8 @@ def main():
     ap.add_argument("--e2e-layers", type=int, default=-1,
                     help="decoder layers streamed from host per e2e step (-1: the whole set at one GPU when host memory allows, else 4)")
     args = ap.parse_args()
+    if args.e2e_layers == 0:
+        args.e2e_layers = 1  # the end-to-end leg is part of the output line: it always streams at least one layer
     if args.impl == "reference":
         return run_reference(args)
 
