@@ -726,6 +726,8 @@ def run_e2e(args, lib, dev, rank, world, mine):
     layers = [t for t in mine if ".layers." in t[0]]
     keep = {n for n, _, _ in layers[: 7 * layers_req]} if layers_req < 32 else None
     sub = sorted([t for t in mine if keep is None or t[0] in keep], key=lambda t: t[0])
+    if not sub:
+        sub = list(mine[:1])  # a rank whose share holds no decoder-layer tensor (short sets over many ranks) streams what it has
     n_sub = sum(r * c for _, r, c in sub)
     h_in = [torch.empty(r * c, dtype=torch.bfloat16).pin_memory() for _, r, c in sub]
     gcpu = torch.Generator().manual_seed(7 + rank)
