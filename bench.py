@@ -503,7 +503,8 @@ def nf4_leg(args, lib, dev, rank, world, arena, codes, barrier, stream):
     for n in mine:
         offs.append(o)
         o += (n + 16383) // 16384 * 16384
-    assert o <= arena.numel()
+    if o > arena.numel():  # a shortened set (--layers) leaves an arena smaller than this rank's share of the 7B-shaped set
+        return {"skipped": "the weight arena of this run is smaller than the NF4 set's share per rank"}
     nb_tot = o // 64
     a8 = torch.empty(max(nb_tot, 1), dtype=torch.uint8, device=dev)
     a2 = torch.empty(nb_tot // 256 + len(mine) + 1, dtype=torch.float32, device=dev)

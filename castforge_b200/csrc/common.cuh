@@ -31,6 +31,7 @@ enum Tunable {
   kTuneA1BarSleep = 9, // persistent A1: nanoseconds between two polls of the grid barrier (0 = poll back to back)
   kTuneA1TailFirst = 10, // persistent A1: the quantize pass re-reads the lines kept in L2 before the ones that were let go
   kTuneGemmPair = 11,  // tensor-core GEMMs: two CTAs (a cluster, two SMs) per 256 x 256 tile where the shape has one
+  kTuneColparP2P = 12, // column-parallel products: 1 = blocks rejoined by this library's peer-load kernel where the ranks can map each other's memory, 0 = always NCCL all-gather
   kTuneCount
 };
 long long tunable(int id);

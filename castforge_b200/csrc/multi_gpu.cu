@@ -13,11 +13,18 @@
 // The reference only stamps `castforge.all_gather` / `castforge.all_reduce` attributes on its graph
 // (src/passes/distributed/spmd.rs:416-478) and evaluates them as the identity (src/codegen/eval.rs:1449-1455); there is
 // no communication code to follow.  NCCL is opened at run time (dlopen of libnccl.so.2), so the library loads and every
-// single-GPU entry point works on a machine without NCCL; only the calls below need it.  No kernel here is handed a
-// pointer into another GPU's memory.
+// single-GPU entry point works on a machine without NCCL; only the calls below need it.
+//
+// Rejoining the column-parallel blocks.  Where the ranks are separate processes on one node, every rank keeps its GEMM
+// output block in a buffer the others have mapped (CUDA IPC), and after one small all-reduce (the "every block is
+// complete" barrier) a copy kernel of this library reads the peers' blocks over NVLink with plain 16-byte loads and
+// writes them straight to their columns of the row-major result: one pass over the product instead of NCCL's all-gather
+// into a staging area plus an interleave pass.  No TMA, no multicast, no library kernel ever sees a peer pointer; if the
+// mapping cannot be set up (ranks in one process, no peer access) the NCCL path is what runs.
 #include <dlfcn.h>
 #include <nccl.h>
 #include <string.h>
+#include <unistd.h>
 
 #include <algorithm>
 #include <mutex>
@@ -31,6 +38,16 @@ struct cfb200_comm {
   // a side stream for small collectives that should not sit in the caller's stream between two kernels
   cudaStream_t side = nullptr;
   cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  // exchange buffer for the column-parallel products: two halves used by alternate calls, mapped by every peer
+  static constexpr int kMaxPeers = 16;
+  int xstate = 0;                 // 0 = not tried yet, 1 = mapped everywhere, -1 = not available (NCCL all-gather instead)
+  void* xlocal = nullptr;         // this rank's buffer (cudaMalloc), 2 * xhalf bytes
+  size_t xhalf = 0;
+  void* xpeer[kMaxPeers] = {};    // xpeer[r] = rank r's buffer as mapped here (xpeer[rank] == xlocal)
+  std::vector<void*> xretired;    // outgrown buffers and their mappings, released with the communicator
+  std::vector<void*> xretired_maps;
+  int32_t* xtick = nullptr;       // one device word for the barrier all-reduce
+  unsigned xcalls = 0;
 };
 
 namespace cfb {
@@ -100,6 +117,140 @@ __global__ void interleave_blocks_kernel(const uint4* __restrict__ gathered, uin
 }
 
 inline size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+// ---- peer-mapped exchange buffer ----------------------------------------------------------------------------------------
+struct XInfo {
+  cudaIpcMemHandle_t handle;
+  int32_t pid, ok;
+};
+
+// Collective over the communicator: makes sure every rank owns an exchange buffer of 2 * half_bytes that every other rank
+// has mapped.  Leaves comm->xstate at 1 (mapped) or -1 (fall back to NCCL) -- the same value on every rank.
+int32_t ensure_exchange(cfb200_comm* comm, size_t half_bytes, cudaStream_t st) {
+  if (comm->xstate < 0) return CFB200_OK;
+  if (comm->xstate == 1 && comm->xhalf >= half_bytes) return CFB200_OK;
+  const NcclApi* api;
+  int32_t rc = nccl_api(&api);
+  if (rc) return rc;
+  const int W = comm->world;
+  if (W > cfb200_comm::kMaxPeers) { comm->xstate = -1; return CFB200_OK; }
+  // the buffers in use go on the retired list (a peer may still be reading them); they are released with the communicator
+  if (comm->xlocal) {
+    comm->xretired.push_back(comm->xlocal);
+    for (int r = 0; r < W; ++r)
+      if (r != comm->rank && comm->xpeer[r]) comm->xretired_maps.push_back(comm->xpeer[r]);
+    comm->xlocal = nullptr;
+    for (int r = 0; r < W; ++r) comm->xpeer[r] = nullptr;
+  }
+  const size_t half = align256(half_bytes + half_bytes / 4);  // some headroom: growing is a collective with two host round trips
+  XInfo mine;
+  memset(&mine, 0, sizeof mine);
+  mine.pid = (int32_t)getpid();
+  mine.ok = 1;
+  void* buf = nullptr;
+  if (cudaMalloc(&buf, 2 * half) != cudaSuccess) { cudaGetLastError(); mine.ok = 0; }
+  if (mine.ok && cudaIpcGetMemHandle(&mine.handle, buf) != cudaSuccess) { cudaGetLastError(); mine.ok = 0; }
+  if (!comm->xtick) {
+    CFB_CUDA(cudaMalloc(reinterpret_cast<void**>(&comm->xtick), 256));
+    CFB_CUDA(cudaMemsetAsync(comm->xtick, 0, 256, st));
+  }
+  // every rank's record to every rank (through device memory: NCCL moves device buffers)
+  XInfo* dev_all = nullptr;
+  CFB_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev_all), sizeof(XInfo) * W));
+  CFB_CUDA(cudaMemcpyAsync(dev_all + comm->rank, &mine, sizeof mine, cudaMemcpyHostToDevice, st));
+  CFB_NCCL(api, api->AllGather(dev_all + comm->rank, dev_all, sizeof(XInfo), ncclInt8, comm->nccl, st));
+  std::vector<XInfo> all(W);
+  CFB_CUDA(cudaMemcpyAsync(all.data(), dev_all, sizeof(XInfo) * W, cudaMemcpyDeviceToHost, st));
+  CFB_CUDA(cudaStreamSynchronize(st));
+  int good = 1;
+  for (int r = 0; r < W; ++r) {
+    if (!all[r].ok) good = 0;
+    if (r != comm->rank && all[r].pid == mine.pid) good = 0;  // ranks inside one process: an IPC handle cannot be opened there
+  }
+  void* maps[cfb200_comm::kMaxPeers] = {};
+  if (good) {
+    for (int r = 0; r < W && good; ++r) {
+      if (r == comm->rank) { maps[r] = buf; continue; }
+      if (cudaIpcOpenMemHandle(&maps[r], all[r].handle, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        cudaGetLastError();
+        maps[r] = nullptr;
+        good = 0;
+      }
+    }
+  }
+  // agree: one rank that could not map means nobody uses the mapping
+  int32_t vote = good;
+  CFB_CUDA(cudaMemcpyAsync(dev_all, &vote, sizeof vote, cudaMemcpyHostToDevice, st));
+  CFB_NCCL(api, api->AllReduce(dev_all, dev_all, 1, ncclInt32, ncclMin, comm->nccl, st));
+  CFB_CUDA(cudaMemcpyAsync(&vote, dev_all, sizeof vote, cudaMemcpyDeviceToHost, st));
+  CFB_CUDA(cudaStreamSynchronize(st));
+  cudaFree(dev_all);
+  if (vote == 1) {
+    comm->xlocal = buf;
+    comm->xhalf = half;
+    for (int r = 0; r < W; ++r) comm->xpeer[r] = maps[r];
+    comm->xstate = 1;
+  } else {
+    for (int r = 0; r < W; ++r)
+      if (r != comm->rank && maps[r]) cudaIpcCloseMemHandle(maps[r]);
+    if (buf) cudaFree(buf);
+    comm->xstate = -1;
+  }
+  return CFB200_OK;
+}
+
+struct PullArgs {
+  const uint4* src[cfb200_comm::kMaxPeers];
+};
+// every rank's [M, Nl] block (in that rank's exchange buffer, read through its mapping here) -> this rank's result:
+// row-major [M][world * Nl] (layout 0) or [world][M][Nl] (layout 1).  16 bytes per load, four loads in flight per thread;
+// consecutive threads read consecutive vectors of one block row, consecutive rows come from different ranks.
+__global__ void __launch_bounds__(256) pull_blocks_kernel(PullArgs a, uint4* __restrict__ out, size_t M, size_t vpr, int world, int layout) {
+  const size_t total = (size_t)world * M * vpr;
+  const size_t step = (size_t)gridDim.x * blockDim.x;
+  for (size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * step) {
+    uint4 v[4];
+    size_t dst[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const size_t i = i0 + u * step;
+      if (i < total) {
+        const size_t vv = i % vpr, mr = i / vpr;
+        const size_t r = mr % world, m = mr / world;
+        v[u] = a.src[r][m * vpr + vv];
+        dst[u] = layout == 0 ? (m * world + r) * vpr + vv : (r * M + m) * vpr + vv;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i0 + u * step < total) out[dst[u]] = v[u];
+  }
+}
+
+// The block this rank is about to compute goes here (nullptr: no mapped exchange buffer, use the caller's workspace).
+void* exchange_slot(cfb200_comm* comm) {
+  if (comm->xstate != 1) return nullptr;
+  return static_cast<char*>(comm->xlocal) + (size_t)(comm->xcalls & 1u) * comm->xhalf;
+}
+
+// After the local block has been written to exchange_slot(): barrier, then pull every block into C.
+int32_t pull_columns(cfb200_comm* comm, size_t M, size_t Nl, size_t elem_bytes, void* C, int32_t layout, cudaStream_t st) {
+  const NcclApi* api;
+  int32_t rc = nccl_api(&api);
+  if (rc) return rc;
+  // every rank's block is complete (and everybody has finished reading the other half, which the next call overwrites)
+  CFB_NCCL(api, api->AllReduce(comm->xtick, comm->xtick, 1, ncclInt32, ncclSum, comm->nccl, st));
+  PullArgs a;
+  const size_t off = (size_t)(comm->xcalls & 1u) * comm->xhalf;
+  for (int r = 0; r < comm->world; ++r) a.src[r] = reinterpret_cast<const uint4*>(static_cast<const char*>(comm->xpeer[r]) + off);
+  const size_t vpr = Nl * elem_bytes / 16;
+  const size_t total = (size_t)comm->world * M * vpr;
+  size_t blocks = (total / 4 + 255) / 256 + 1, cap = (size_t)sm_count() * 8;
+  pull_blocks_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(a, reinterpret_cast<uint4*>(C), M, vpr, comm->world, layout);
+  CFB_LAUNCH_CHECK();
+  ++comm->xcalls;
+  return CFB200_OK;
+}
 
 // local [M, Nl] block (elem_bytes per element) -> every rank's C [M, world * Nl] (layout 0) or [world][M][Nl] (layout 1)
 int32_t gather_columns(cfb200_comm* comm, const void* part, size_t M, size_t Nl, size_t elem_bytes, void* C, int32_t layout,
@@ -185,6 +336,24 @@ extern "C" int32_t cfb200_comm_rank(const cfb200_comm* comm) { return comm ? com
 extern "C" void cfb200_comm_free(cfb200_comm* comm) {
   if (!comm) return;
   const NcclApi* api;
+  if (comm->xlocal || !comm->xretired.empty()) {
+    // mappings of the peers' buffers go first; a buffer may only be freed once nobody has it mapped any more, which the
+    // all-reduce tells (every rank passes through here when the communicator is torn down)
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaSetDevice(comm->device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < comm->world && r < cfb200_comm::kMaxPeers; ++r)
+      if (r != comm->rank && comm->xpeer[r]) cudaIpcCloseMemHandle(comm->xpeer[r]);
+    for (void* m : comm->xretired_maps) cudaIpcCloseMemHandle(m);
+    if (comm->nccl && comm->xtick && nccl_api(&api) == CFB200_OK &&
+        api->AllReduce(comm->xtick, comm->xtick, 1, ncclInt32, ncclSum, comm->nccl, nullptr) == ncclSuccess)
+      cudaStreamSynchronize(nullptr);
+    if (comm->xlocal) cudaFree(comm->xlocal);
+    for (void* b : comm->xretired) cudaFree(b);
+    cudaSetDevice(dev);
+  }
+  if (comm->xtick) cudaFree(comm->xtick);
   if (comm->nccl && nccl_api(&api) == CFB200_OK) api->CommDestroy(comm->nccl);
   if (comm->ev_fork) cudaEventDestroy(comm->ev_fork);
   if (comm->ev_join) cudaEventDestroy(comm->ev_join);
@@ -323,15 +492,21 @@ extern "C" int32_t cfb200_gemm_w4a16_colpar(cfb200_comm* comm, const void* A, co
   if (!workspace || workspace_bytes < need) return set_error(CFB200_ERR_WORKSPACE, "gemm_w4a16_colpar needs %zu bytes of workspace", need);
   char* ws = reinterpret_cast<char*>(workspace);
   const size_t out_bytes = align256(M * N_local * 2);
-  void* part = ws;
   void* gathered = ws + out_bytes;
   const bool has_gather = comm->world > 1 && M > 1;
   void* inner = ws + out_bytes + (has_gather ? align256(out_bytes * comm->world) : 0);
   int32_t rc;
+  if (has_gather && tunable(kTuneColparP2P) != 0) {
+    rc = ensure_exchange(comm, out_bytes, (cudaStream_t)stream);
+    if (rc) return rc;
+  }
+  void* slot = (has_gather && tunable(kTuneColparP2P) != 0) ? exchange_slot(comm) : nullptr;
+  void* part = slot ? slot : ws;
   if (M <= 16 && group == 128) rc = cfb200_gemv_w4a16(A, w_codes, w_scales, w_zps, M, N_local, K, group, part, 0, stream);
   else rc = cfb200_gemm_w4a16(A, w_codes, w_scales, w_zps, M, N_local, K, group, part, 0, inner,
                               cfb200_gemm_w4a16_workspace_bytes(M, N_local, K), error_flag, stream);
   if (rc) return rc;
+  if (slot) return pull_columns(comm, M, N_local, 2, C, layout, (cudaStream_t)stream);
   return gather_columns(comm, part, M, N_local, 2, C, layout, gathered, (cudaStream_t)stream);
 }
 
@@ -347,8 +522,16 @@ extern "C" int32_t cfb200_gemm_fp8_colpar(cfb200_comm* comm, const uint8_t* A, c
   if (!workspace || workspace_bytes < need) return set_error(CFB200_ERR_WORKSPACE, "gemm_fp8_colpar needs %zu bytes of workspace", need);
   char* ws = reinterpret_cast<char*>(workspace);
   const size_t out_bytes = align256(M * N_local * 2);
-  int32_t rc = cfb200_gemm_fp8(A, a_scales, W_local, w_scale, M, N_local, K, ws, 0, error_flag, stream);
+  const bool p2p = comm->world > 1 && M > 1 && tunable(kTuneColparP2P) != 0;
+  int32_t rc;
+  if (p2p) {
+    rc = ensure_exchange(comm, out_bytes, (cudaStream_t)stream);
+    if (rc) return rc;
+  }
+  void* slot = p2p ? exchange_slot(comm) : nullptr;
+  rc = cfb200_gemm_fp8(A, a_scales, W_local, w_scale, M, N_local, K, slot ? slot : ws, 0, error_flag, stream);
   if (rc) return rc;
+  if (slot) return pull_columns(comm, M, N_local, 2, C, layout, (cudaStream_t)stream);
   return gather_columns(comm, ws, M, N_local, 2, C, layout, ws + out_bytes, (cudaStream_t)stream);
 }
 

@@ -29,8 +29,8 @@ int sm_count() {
   return cached[dev];
 }
 
-static long long g_tunables[kTuneCount] = {0, 0, 0, 1, 0, 60, 1, 0, 0, 0, 1, 1};  // a1_persist on; 60 MB of a group's tail kept in L2 and re-read first
-static const char* const kTunableNames[kTuneCount] = {"a1_keep_mb", "a1_demote", "a1_merge", "a1_persist", "a1_group_mb", "a1_retain_mb", "gemv_ring", "gemv_ring_rounds", "w4_split_k", "a1_bar_sleep", "a1_tail_first", "gemm_pair"};
+static long long g_tunables[kTuneCount] = {0, 0, 0, 1, 0, 60, 1, 0, 0, 0, 1, 1, 1};  // a1_persist on; 60 MB of a group's tail kept in L2 and re-read first
+static const char* const kTunableNames[kTuneCount] = {"a1_keep_mb", "a1_demote", "a1_merge", "a1_persist", "a1_group_mb", "a1_retain_mb", "gemv_ring", "gemv_ring_rounds", "w4_split_k", "a1_bar_sleep", "a1_tail_first", "gemm_pair", "colpar_p2p"};
 
 long long tunable(int id) { return (id >= 0 && id < kTuneCount) ? g_tunables[id] : 0; }
 
