@@ -227,6 +227,15 @@ __global__ void __launch_bounds__(256) pull_blocks_kernel(PullArgs a, uint4* __r
   }
 }
 
+// Small products stay with NCCL's all-gather: the barrier all-reduce in front of the peer loads costs about as much as
+// the whole all-gather of a few hundred KB per rank (decode shapes).  "colpar_p2p": 0 = never, 1 = from 8 MB of product,
+// n > 1 = from n MB.
+bool use_peer_loads(size_t block_bytes, int world) {
+  const long long knob = tunable(kTuneColparP2P);
+  if (knob == 0) return false;
+  return block_bytes * (size_t)world >= ((size_t)(knob == 1 ? 8 : knob) << 20);
+}
+
 // The block this rank is about to compute goes here (nullptr: no mapped exchange buffer, use the caller's workspace).
 void* exchange_slot(cfb200_comm* comm) {
   if (comm->xstate != 1) return nullptr;
@@ -496,11 +505,12 @@ extern "C" int32_t cfb200_gemm_w4a16_colpar(cfb200_comm* comm, const void* A, co
   const bool has_gather = comm->world > 1 && M > 1;
   void* inner = ws + out_bytes + (has_gather ? align256(out_bytes * comm->world) : 0);
   int32_t rc;
-  if (has_gather && tunable(kTuneColparP2P) != 0) {
+  const bool p2p = has_gather && use_peer_loads(out_bytes, comm->world);
+  if (p2p) {
     rc = ensure_exchange(comm, out_bytes, (cudaStream_t)stream);
     if (rc) return rc;
   }
-  void* slot = (has_gather && tunable(kTuneColparP2P) != 0) ? exchange_slot(comm) : nullptr;
+  void* slot = p2p ? exchange_slot(comm) : nullptr;
   void* part = slot ? slot : ws;
   if (M <= 16 && group == 128) rc = cfb200_gemv_w4a16(A, w_codes, w_scales, w_zps, M, N_local, K, group, part, 0, stream);
   else rc = cfb200_gemm_w4a16(A, w_codes, w_scales, w_zps, M, N_local, K, group, part, 0, inner,
@@ -522,7 +532,7 @@ extern "C" int32_t cfb200_gemm_fp8_colpar(cfb200_comm* comm, const uint8_t* A, c
   if (!workspace || workspace_bytes < need) return set_error(CFB200_ERR_WORKSPACE, "gemm_fp8_colpar needs %zu bytes of workspace", need);
   char* ws = reinterpret_cast<char*>(workspace);
   const size_t out_bytes = align256(M * N_local * 2);
-  const bool p2p = comm->world > 1 && M > 1 && tunable(kTuneColparP2P) != 0;
+  const bool p2p = comm->world > 1 && M > 1 && use_peer_loads(out_bytes, comm->world);
   int32_t rc;
   if (p2p) {
     rc = ensure_exchange(comm, out_bytes, (cudaStream_t)stream);

@@ -57,7 +57,9 @@ const char* cfb200_version(void);
  * with M <= 256: 0 = automatic split-K, 1 = never, n = at most n slices; changes the summation
  * order of the f32 accumulation and nothing else), "gemm_pair" (the bf16 / FP8 / W4A16-prefill products: 1, default =
  * two CTAs of a cluster (two SMs, tcgen05 cta_group::2) per 256 x 256 tile where the product has at least 56 such tiles
- * (W4A16: M > 256 and 32 tiles); 0 = always one CTA per tile; 2 = pairs wherever M > 128 (W4A16: M > 256). */
+ * (W4A16: M > 256 and 32 tiles); 0 = always one CTA per tile; 2 = pairs wherever M > 128 (W4A16: M > 256)), "colpar_p2p"
+ * (column-parallel products: 1, default = products of 8 MB and more are rejoined by a peer-load kernel over CUDA-IPC
+ * mappings where the ranks are separate processes on one node; 0 = always ncclAllGather; n > 1 = from n MB). */
 int32_t cfb200_tune(const char* key, int64_t value);
 
 /* ---- A1: per-tensor symmetric INT8 / INT4 ------------------------------------------------
@@ -384,10 +386,16 @@ int32_t cfb200_gptq_hessian_scaled(const void* X, size_t T, size_t K, float alph
  *
  * Column-parallel GEMMs: every rank holds N_local = N / world rows of the [N, K] weight (rank r: rows
  *  [r N_local, (r + 1) N_local), with their scales and zero points) and the whole activation matrix.  The rank's block of
- *  the product comes from cfb200_gemm_w4a16 (cfb200_gemv_w4a16 when M <= 16 and group == 128) or cfb200_gemm_fp8; one
- *  ncclAllGather then leaves the whole bf16 product in C on every rank: layout 0 = row-major [M, N] (the gathered
- *  blocks are interleaved by one more launch when M > 1), layout 1 = [world][M][N_local] as gathered.
- *  N_local % 8 == 0; workspace (256-byte aligned) of cfb200_gemm_colpar_workspace_bytes(..., w4 = 1 or 0).
+ *  the product comes from cfb200_gemm_w4a16 (cfb200_gemv_w4a16 when M <= 16 and group == 128) or cfb200_gemm_fp8; the
+ *  blocks are then rejoined so that every rank holds the whole bf16 product in C: layout 0 = row-major [M, N], layout 1 =
+ *  [world][M][N_local].  Products of 8 MB and more between ranks that are separate processes on one node: the blocks are
+ *  written to exchange buffers that the library allocates and the ranks map from one another (CUDA IPC; set up by the
+ *  first call of a shape class, which synchronises the stream and must not run under stream capture), one small
+ *  all-reduce says that every block is complete, and a copy kernel reads the peers' blocks over NVLink straight into C.
+ *  Otherwise: one ncclAllGather (plus one interleaving launch for layout 0 with M > 1).  Either way the bits in C are
+ *  the local kernels' bits.  N_local % 8 == 0; workspace (256-byte aligned) of
+ *  cfb200_gemm_colpar_workspace_bytes(..., w4 = 1 or 0).  Calls on one communicator are issued in the same order on
+ *  every rank (as for any collective).
  *
  * cfb200_gptq_hessian_sharded: every rank passes its T_local calibration tokens (T_local % 8 == 0, may be 0); H receives
  *  X^T X / T_total summed over ranks (one ncclAllReduce of K x K floats).  The factor U is then computed on every rank
