@@ -229,10 +229,11 @@ __global__ void __launch_bounds__(256) pull_blocks_kernel(PullArgs a, uint4* __r
 
 // Small products stay with NCCL's all-gather: the barrier all-reduce in front of the peer loads costs about as much as
 // the whole all-gather of a few hundred KB per rank (decode shapes).  "colpar_p2p": 0 = never, 1 = from 8 MB of product,
-// n > 1 = from n MB.
+// n > 1 = from n MB, negative = always.
 bool use_peer_loads(size_t block_bytes, int world) {
   const long long knob = tunable(kTuneColparP2P);
   if (knob == 0) return false;
+  if (knob < 0) return true;
   return block_bytes * (size_t)world >= ((size_t)(knob == 1 ? 8 : knob) << 20);
 }
 

@@ -59,7 +59,8 @@ const char* cfb200_version(void);
  * two CTAs of a cluster (two SMs, tcgen05 cta_group::2) per 256 x 256 tile where the product has at least 56 such tiles
  * (W4A16: M > 256 and 32 tiles); 0 = always one CTA per tile; 2 = pairs wherever M > 128 (W4A16: M > 256)), "colpar_p2p"
  * (column-parallel products: 1, default = products of 8 MB and more are rejoined by a peer-load kernel over CUDA-IPC
- * mappings where the ranks are separate processes on one node; 0 = always ncclAllGather; n > 1 = from n MB). */
+ * mappings where the ranks are separate processes on one node; 0 = always ncclAllGather; n > 1 = from n MB; negative =
+ * peer loads for every size). */
 int32_t cfb200_tune(const char* key, int64_t value);
 
 /* ---- A1: per-tensor symmetric INT8 / INT4 ------------------------------------------------

@@ -28,6 +28,21 @@ def shard_w4(codes, scales, zps, N, K, lo, hi, group=128):
 
 
 def check_colpar(comm, dev, rank, world):
+    """Both ways of rejoining the blocks: ncclAllGather + interleave (knob 0) and the peer-load kernel over the ranks'
+    IPC-mapped exchange buffers (knob -1: for every size; the default takes it from 8 MB of product)."""
+    import castforge_b200
+    lib = castforge_b200.load()
+    try:
+        for knob in (0, -1):
+            assert lib.cfb200_tune(b"colpar_p2p", knob) == 0
+            check_colpar_once(comm, dev, rank, world)
+            check_colpar_once(comm, dev, rank, world)      # again: the exchange buffer's other half
+    finally:
+        lib.cfb200_tune(b"colpar_p2p", 1)
+    return True
+
+
+def check_colpar_once(comm, dev, rank, world):
     import castforge_b200
     from castforge_b200 import device as cf, multi_gpu as mg
     lib = castforge_b200.load()
