@@ -347,8 +347,10 @@ extern "C" void cfb200_comm_free(cfb200_comm* comm) {
   if (!comm) return;
   const NcclApi* api;
   if (comm->xlocal || !comm->xretired.empty()) {
-    // mappings of the peers' buffers go first; a buffer may only be freed once nobody has it mapped any more, which the
-    // all-reduce tells (every rank passes through here when the communicator is torn down)
+    // This rank's mappings of the peers' buffers are closed.  Its OWN exchange buffers stay allocated until the process
+    // ends: a buffer may only be freed once no peer has it mapped, and learning that would take a collective here -- which
+    // would hang the ranks that are shutting down cleanly whenever another rank has failed.  (One buffer pair per
+    // communicator that ever ran a large column-parallel product.)
     int dev = 0;
     cudaGetDevice(&dev);
     cudaSetDevice(comm->device);
@@ -356,11 +358,6 @@ extern "C" void cfb200_comm_free(cfb200_comm* comm) {
     for (int r = 0; r < comm->world && r < cfb200_comm::kMaxPeers; ++r)
       if (r != comm->rank && comm->xpeer[r]) cudaIpcCloseMemHandle(comm->xpeer[r]);
     for (void* m : comm->xretired_maps) cudaIpcCloseMemHandle(m);
-    if (comm->nccl && comm->xtick && nccl_api(&api) == CFB200_OK &&
-        api->AllReduce(comm->xtick, comm->xtick, 1, ncclInt32, ncclSum, comm->nccl, nullptr) == ncclSuccess)
-      cudaStreamSynchronize(nullptr);
-    if (comm->xlocal) cudaFree(comm->xlocal);
-    for (void* b : comm->xretired) cudaFree(b);
     cudaSetDevice(dev);
   }
   if (comm->xtick) cudaFree(comm->xtick);
