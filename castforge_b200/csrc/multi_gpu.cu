@@ -205,14 +205,18 @@ struct PullArgs {
 // every rank's [M, Nl] block (in that rank's exchange buffer, read through its mapping here) -> this rank's result:
 // row-major [M][world * Nl] (layout 0) or [world][M][Nl] (layout 1).  16 bytes per load, four loads in flight per thread;
 // consecutive threads read consecutive vectors of one block row, consecutive rows come from different ranks.
+#ifndef CFB_PULL_INFLIGHT
+#define CFB_PULL_INFLIGHT 4
+#endif
+constexpr int kPullInFlight = CFB_PULL_INFLIGHT;  // 16-byte loads a thread has in flight
 __global__ void __launch_bounds__(256) pull_blocks_kernel(PullArgs a, uint4* __restrict__ out, size_t M, size_t vpr, int world, int layout) {
   const size_t total = (size_t)world * M * vpr;
   const size_t step = (size_t)gridDim.x * blockDim.x;
-  for (size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * step) {
-    uint4 v[4];
-    size_t dst[4];
+  for (size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += kPullInFlight * step) {
+    uint4 v[kPullInFlight];
+    size_t dst[kPullInFlight];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < kPullInFlight; ++u) {
       const size_t i = i0 + u * step;
       if (i < total) {
         const size_t vv = i % vpr, mr = i / vpr;
@@ -222,7 +226,7 @@ __global__ void __launch_bounds__(256) pull_blocks_kernel(PullArgs a, uint4* __r
       }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u)
+    for (int u = 0; u < kPullInFlight; ++u)
       if (i0 + u * step < total) out[dst[u]] = v[u];
   }
 }
@@ -255,7 +259,7 @@ int32_t pull_columns(cfb200_comm* comm, size_t M, size_t Nl, size_t elem_bytes, 
   for (int r = 0; r < comm->world; ++r) a.src[r] = reinterpret_cast<const uint4*>(static_cast<const char*>(comm->xpeer[r]) + off);
   const size_t vpr = Nl * elem_bytes / 16;
   const size_t total = (size_t)comm->world * M * vpr;
-  size_t blocks = (total / 4 + 255) / 256 + 1, cap = (size_t)sm_count() * 8;
+  size_t blocks = (total / kPullInFlight + 255) / 256 + 1, cap = (size_t)sm_count() * 8;
   pull_blocks_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, st>>>(a, reinterpret_cast<uint4*>(C), M, vpr, comm->world, layout);
   CFB_LAUNCH_CHECK();
   ++comm->xcalls;
