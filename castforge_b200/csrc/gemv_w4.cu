@@ -285,6 +285,13 @@ static __device__ int g_gv_flag;  // sticky: a bounded wait of the ring kernel r
 #define CFB_GV_SLOTS 3
 #endif
 constexpr int kWarpsM8 = CFB_GV_WARPS;  // warps per CTA for M <= 8 (M = 9..16: 8 warps, the activations take twice the room)
+#ifndef CFB_GV_M16_WARPS
+#define CFB_GV_M16_WARPS 8
+#endif
+#ifndef CFB_GV_M16_SLOTS
+#define CFB_GV_M16_SLOTS 2
+#endif
+constexpr int kWarpsM16 = CFB_GV_M16_WARPS, kSlotsM16 = CFB_GV_M16_SLOTS;  // M = 9..16
 constexpr int kItemChunks = 4;               // 128-k groups per item
 constexpr int kBoxBytes = 16 * 128;          // one TMA box: 16 rows x 128 bytes, 128-byte swizzle
 constexpr int kSlotBytes = 2 * kBoxBytes;    // an item = two boxes side by side along K
@@ -645,7 +652,7 @@ EncodeTiledFn encode_fn() {
 // Ring kernel launch; returns CFB200_ERR_UNSUPPORTED when the shape does not fit it.
 template <int MT, int kW5>
 int32_t launch_gv_ring(const GvArgs& a, cudaStream_t st) {
-  constexpr int kSlots = MT == 1 ? kSlotsM8 : 2;
+  constexpr int kSlots = MT == 1 ? kSlotsM8 : kSlotsM16;
   constexpr int kT5 = kW5 * 32;
   const int gpr = a.K / kChunk;
   if (gpr % kItemChunks != 0) return CFB200_ERR_UNSUPPORTED;
@@ -760,7 +767,7 @@ extern "C" int32_t cfb200_gemv_w4a16(const void* A, const uint8_t* w_codes, cons
       rc = best_w == kWarpsM8 ? launch_gv_ring<1, kWarpsM8>(a, st)
            : best_w == kWarpsM8 - 1 ? launch_gv_ring<1, kWarpsM8 - 1>(a, st) : launch_gv_ring<1, kWarpsM8 - 2>(a, st);
     } else {
-      rc = launch_gv_ring<2, 8>(a, st);
+      rc = launch_gv_ring<2, kWarpsM16>(a, st);
     }
     if (rc != CFB200_ERR_UNSUPPORTED) return rc;
   }
