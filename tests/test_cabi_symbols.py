@@ -37,6 +37,13 @@ def test_version_and_error_string_without_gpu():
     assert rc == 1 and b"group" in lib.cfb200_last_error()
     rc = lib.cfb200_quant_sym_tensor(ctypes.c_void_p(4), 0, 16, 8, ctypes.c_void_p(16), ctypes.c_void_p(16), None)
     assert rc == 2  # misaligned source
+    # the bf16 product with row pitches: a pitch shorter than the row, an unknown triangle selector, C += into a bf16 result
+    p = ctypes.c_void_p(256)
+    assert lib.cfb200_gemm_bf16_nt_ex(p, 64, p, 64, 128, 128, 64, 1.0, p, 64, 1, 0, 0, None, None) == 1 and b"pitch" in lib.cfb200_last_error()
+    assert lib.cfb200_gemm_bf16_nt_ex(p, 64, p, 64, 128, 128, 64, 1.0, p, 128, 1, 3, 0, None, None) == 1 and b"triangle" in lib.cfb200_last_error()
+    assert lib.cfb200_gemm_bf16_nt_ex(p, 64, p, 64, 128, 128, 64, 1.0, p, 128, 0, 0, 1, None, None) == 1 and b"f32" in lib.cfb200_last_error()
+    # knobs: known keys are accepted, unknown ones are not
+    assert lib.cfb200_tune(b"gemm_pair", 1) == 0 and lib.cfb200_tune(b"colpar_p2p", 1) == 0 and lib.cfb200_tune(b"no_such_knob", 1) != 0
 
 
 def test_product_does_not_reference_the_oracle():
