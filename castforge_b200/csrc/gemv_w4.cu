@@ -233,37 +233,58 @@ gemv_w4_kernel(const GvArgs a, int tiles_per_warp, int cpc /* chunks per CTA */,
     }
   }
 
-  // this CTA's partial sums -> its own shared memory, then the cluster adds them up over DSMEM
+  // Reduction over the cluster's K split.  Every CTA finishes `share` of the cluster's rows: the others PUSH their partial
+  // sums for those rows into its shared memory (slot = sender's rank; posted stores over DSMEM), one cluster barrier makes
+  // them visible, and the owner adds the slots up from its own memory.  (Pulling the partial sums instead took a second
+  // barrier -- nobody may leave while its memory is still being read -- and a round trip per remote value.)
   GV_STAMP(2);
-#pragma unroll
-  for (int ti = 0; ti < kMaxTiles; ++ti) {
-    if (ti >= tiles_per_warp) break;
-#pragma unroll
-    for (int mh = 0; mh < MT; ++mh) {
-      float* base = part + (size_t)((ti * kWarps + warp) * 16) * kCols + mh * 8;
-      base[(g)*kCols + 2 * t] = total[ti][mh][0];
-      base[(g)*kCols + 2 * t + 1] = total[ti][mh][1];
-      base[(g + 8) * kCols + 2 * t] = total[ti][mh][2];
-      base[(g + 8) * kCols + 2 * t + 1] = total[ti][mh][3];
-    }
-  }
-  if (csize > 1) cluster_sync_all(); else __syncthreads();
   const int share = rows_per_cluster / csize;  // rows this CTA finishes (rows_per_cluster is a multiple of 64)
-  for (int o = threadIdx.x; o < share * kCols; o += kThreadsGv) {
-    const int m = o / share, r = (int)rank * share + o % share;  // consecutive threads -> consecutive n
-    const int n = row0 + r;
-    float sum = 0.0f;
-    if (csize > 1) {
-      for (uint32_t q = 0; q < (uint32_t)csize; ++q) sum += ld_dsmem_f32(part + (size_t)r * kCols + m, q);
-    } else {
-      sum = part[(size_t)r * kCols + m];
+  if (csize > 1) {
+    const uint32_t part_addr = (uint32_t)__cvta_generic_to_shared(part);
+#pragma unroll
+    for (int ti = 0; ti < kMaxTiles; ++ti) {
+      if (ti >= tiles_per_warp) break;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int r = (ti * kWarps + warp) * 16 + g + 8 * hh;  // row of the cluster
+        const uint32_t owner = (uint32_t)(r / share);
+        uint32_t base;  // owner's slot [rank][r % share][0]
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                     : "=r"(base)
+                     : "r"(part_addr + (uint32_t)((((size_t)rank * share + (size_t)(r % share)) * kCols) * sizeof(float))), "r"(owner));
+#pragma unroll
+        for (int mh = 0; mh < MT; ++mh)
+          asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(base + (uint32_t)((mh * 8 + 2 * t) * sizeof(float))),
+                       "f"(total[ti][mh][2 * hh]), "f"(total[ti][mh][2 * hh + 1])
+                       : "memory");
+      }
     }
+    cluster_sync_all();  // release / acquire at cluster scope: every slot of every CTA is complete and visible
+  } else {
+#pragma unroll
+    for (int ti = 0; ti < kMaxTiles; ++ti) {
+      if (ti >= tiles_per_warp) break;
+#pragma unroll
+      for (int mh = 0; mh < MT; ++mh) {
+        float* base = part + (size_t)((ti * kWarps + warp) * 16) * kCols + mh * 8;
+        base[(g)*kCols + 2 * t] = total[ti][mh][0];
+        base[(g)*kCols + 2 * t + 1] = total[ti][mh][1];
+        base[(g + 8) * kCols + 2 * t] = total[ti][mh][2];
+        base[(g + 8) * kCols + 2 * t + 1] = total[ti][mh][3];
+      }
+    }
+    __syncthreads();
+  }
+  for (int o = threadIdx.x; o < share * kCols; o += kThreadsGv) {
+    const int m = o / share, rl = o % share;  // consecutive threads -> consecutive n
+    const int n = row0 + (int)rank * share + rl;
+    float sum = 0.0f;
+    for (int q = 0; q < csize; ++q) sum += part[((size_t)q * share + rl) * kCols + m];  // csize == 1: slot 0 is the whole block
     if (m < a.M && n < a.N) {
       if (a.out_f32) reinterpret_cast<float*>(a.C)[(size_t)m * a.N + n] = sum;
       else reinterpret_cast<__nv_bfloat16*>(a.C)[(size_t)m * a.N + n] = __float2bfloat16_rn(sum);
     }
   }
-  if (csize > 1) cluster_sync_all();  // nobody leaves while its shared memory may still be read
   GV_STAMP(3);
 }
 
