@@ -148,19 +148,27 @@ int32_t ensure_exchange(cfb200_comm* comm, size_t half_bytes, cudaStream_t st) {
   mine.pid = (int32_t)getpid();
   mine.ok = 1;
   void* buf = nullptr;
-  if (cudaMalloc(&buf, 2 * half) != cudaSuccess) { cudaGetLastError(); mine.ok = 0; }
+  if (cudaMalloc(&buf, 2 * half) != cudaSuccess) { cudaGetLastError(); buf = nullptr; mine.ok = 0; }
+  struct PendingBuffer {  // the new exchange buffer belongs to this function until the ranks have agreed to use it
+    void* p = nullptr;
+    ~PendingBuffer() { if (p) cudaFree(p); }
+  } pending;
+  pending.p = buf;
   if (mine.ok && cudaIpcGetMemHandle(&mine.handle, buf) != cudaSuccess) { cudaGetLastError(); mine.ok = 0; }
   if (!comm->xtick) {
     CFB_CUDA(cudaMalloc(reinterpret_cast<void**>(&comm->xtick), 256));
     CFB_CUDA(cudaMemsetAsync(comm->xtick, 0, 256, st));
   }
   // every rank's record to every rank (through device memory: NCCL moves device buffers)
-  XInfo* dev_all = nullptr;
-  CFB_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev_all), sizeof(XInfo) * W));
-  CFB_CUDA(cudaMemcpyAsync(dev_all + comm->rank, &mine, sizeof mine, cudaMemcpyHostToDevice, st));
-  CFB_NCCL(api, api->AllGather(dev_all + comm->rank, dev_all, sizeof(XInfo), ncclInt8, comm->nccl, st));
+  struct DevScratch {  // released on every way out of this function
+    XInfo* p = nullptr;
+    ~DevScratch() { if (p) cudaFree(p); }
+  } dev_all;
+  CFB_CUDA(cudaMalloc(reinterpret_cast<void**>(&dev_all.p), sizeof(XInfo) * W));
+  CFB_CUDA(cudaMemcpyAsync(dev_all.p + comm->rank, &mine, sizeof mine, cudaMemcpyHostToDevice, st));
+  CFB_NCCL(api, api->AllGather(dev_all.p + comm->rank, dev_all.p, sizeof(XInfo), ncclInt8, comm->nccl, st));
   std::vector<XInfo> all(W);
-  CFB_CUDA(cudaMemcpyAsync(all.data(), dev_all, sizeof(XInfo) * W, cudaMemcpyDeviceToHost, st));
+  CFB_CUDA(cudaMemcpyAsync(all.data(), dev_all.p, sizeof(XInfo) * W, cudaMemcpyDeviceToHost, st));
   CFB_CUDA(cudaStreamSynchronize(st));
   int good = 1;
   for (int r = 0; r < W; ++r) {
@@ -178,23 +186,31 @@ int32_t ensure_exchange(cfb200_comm* comm, size_t half_bytes, cudaStream_t st) {
       }
     }
   }
+  auto close_maps = [&]() {
+    for (int r = 0; r < W; ++r)
+      if (r != comm->rank && maps[r]) { cudaIpcCloseMemHandle(maps[r]); maps[r] = nullptr; }
+  };
   // agree: one rank that could not map means nobody uses the mapping
   int32_t vote = good;
-  CFB_CUDA(cudaMemcpyAsync(dev_all, &vote, sizeof vote, cudaMemcpyHostToDevice, st));
-  CFB_NCCL(api, api->AllReduce(dev_all, dev_all, 1, ncclInt32, ncclMin, comm->nccl, st));
-  CFB_CUDA(cudaMemcpyAsync(&vote, dev_all, sizeof vote, cudaMemcpyDeviceToHost, st));
-  CFB_CUDA(cudaStreamSynchronize(st));
-  cudaFree(dev_all);
+  int32_t* dev_vote = reinterpret_cast<int32_t*>(dev_all.p);
+  bool agreed = cudaMemcpyAsync(dev_vote, &vote, sizeof vote, cudaMemcpyHostToDevice, st) == cudaSuccess &&
+                api->AllReduce(dev_vote, dev_vote, 1, ncclInt32, ncclMin, comm->nccl, st) == ncclSuccess &&
+                cudaMemcpyAsync(&vote, dev_vote, sizeof vote, cudaMemcpyDeviceToHost, st) == cudaSuccess &&
+                cudaStreamSynchronize(st) == cudaSuccess;
+  if (!agreed) {
+    close_maps();
+    comm->xstate = -1;
+    return set_error(CFB200_ERR_CUDA, "the ranks could not agree on the exchange buffers (CUDA or NCCL error)");
+  }
   if (vote == 1) {
     comm->xlocal = buf;
+    pending.p = nullptr;  // kept
     comm->xhalf = half;
     for (int r = 0; r < W; ++r) comm->xpeer[r] = maps[r];
     comm->xstate = 1;
   } else {
-    for (int r = 0; r < W; ++r)
-      if (r != comm->rank && maps[r]) cudaIpcCloseMemHandle(maps[r]);
-    if (buf) cudaFree(buf);
-    comm->xstate = -1;
+    close_maps();
+    comm->xstate = -1;  // (the buffer goes with `pending`)
   }
   return CFB200_OK;
 }
